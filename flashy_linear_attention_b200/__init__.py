@@ -1,0 +1,31 @@
+"""B200-native (sm_100a) causal linear attention behind the `flashlinear` Python API.
+
+Public surface (same names as the reference package, flashlinear/__init__.py:1-2 and
+flashlinear/kernels/__init__.py:1-5):
+    LinearAttention, LinearAttentionSmallVHD,
+    linear_flash_wrapper_fwd, linear_flash_wrapper_bwd,
+    linear_flash_wrapper_fwd_smallv_hd, linear_flash_wrapper_bwd_smallv_hd
+plus the lower-level causal_dot_product_fwd / causal_dot_product_bwd (running-state arguments).
+"""
+from .functions import LinearAttention, LinearAttentionSmallVHD
+from .ops import (
+    causal_dot_product_bwd,
+    causal_dot_product_fwd,
+    check_status,
+    linear_flash_wrapper_bwd,
+    linear_flash_wrapper_bwd_smallv_hd,
+    linear_flash_wrapper_fwd,
+    linear_flash_wrapper_fwd_smallv_hd,
+)
+
+__all__ = [
+    "LinearAttention",
+    "LinearAttentionSmallVHD",
+    "linear_flash_wrapper_fwd",
+    "linear_flash_wrapper_bwd",
+    "linear_flash_wrapper_fwd_smallv_hd",
+    "linear_flash_wrapper_bwd_smallv_hd",
+    "causal_dot_product_fwd",
+    "causal_dot_product_bwd",
+    "check_status",
+]

@@ -1,0 +1,96 @@
+"""ctypes binding of libflashlinear_sm100.so (C ABI in include/flashlinear_sm100.h).
+
+There is no fallback: if the library is missing the import fails with an error that says how to
+build it, and every call fails loudly when the current device is not an sm_100 GPU.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libflashlinear_sm100.so")
+
+FLA_ABI_VERSION = 1
+
+
+class FlaTensor(ctypes.Structure):
+    _fields_ = [
+        ("ptr", ctypes.c_void_p),
+        ("stride_b", ctypes.c_int64),
+        ("stride_h", ctypes.c_int64),
+        ("stride_n", ctypes.c_int64),
+    ]
+
+
+class FlaArgs(ctypes.Structure):
+    _fields_ = [
+        ("batch", ctypes.c_int32),
+        ("heads", ctypes.c_int32),
+        ("seqlen", ctypes.c_int32),
+        ("dk", ctypes.c_int32),
+        ("dv", ctypes.c_int32),
+        ("q", FlaTensor),
+        ("k", FlaTensor),
+        ("v", FlaTensor),
+        ("o", FlaTensor),
+        ("d_o", FlaTensor),
+        ("d_q", FlaTensor),
+        ("d_k", FlaTensor),
+        ("d_v", FlaTensor),
+        ("s_init", ctypes.c_void_p),
+        ("s_final", ctypes.c_void_p),
+        ("r_init", ctypes.c_void_p),
+        ("r_final", ctypes.c_void_p),
+        ("segments", ctypes.c_int32),
+        ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_size_t),
+        ("status", ctypes.c_void_p),
+        ("stream", ctypes.c_void_p),
+    ]
+
+
+EXPORTED_SYMBOLS = (
+    "fla_sm100_abi_version",
+    "fla_sm100_strerror",
+    "fla_sm100_workspace_bytes",
+    "fla_sm100_auto_segments",
+    "fla_sm100_fwd",
+    "fla_sm100_bwd",
+    "fla_sm100_last_launch_count",
+)
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Loads the shared library once; raises ImportError when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing. Build it with `python -m flashy_linear_attention_b200.build` "
+            "(needs nvcc); there is no CPU or PyTorch fallback for these kernels."
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.fla_sm100_abi_version.restype = ctypes.c_int
+    lib.fla_sm100_strerror.restype = ctypes.c_char_p
+    lib.fla_sm100_strerror.argtypes = [ctypes.c_int]
+    lib.fla_sm100_workspace_bytes.restype = ctypes.c_size_t
+    lib.fla_sm100_workspace_bytes.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_int]
+    lib.fla_sm100_auto_segments.restype = ctypes.c_int
+    lib.fla_sm100_auto_segments.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_int]
+    lib.fla_sm100_fwd.restype = ctypes.c_int
+    lib.fla_sm100_fwd.argtypes = [ctypes.POINTER(FlaArgs)]
+    lib.fla_sm100_bwd.restype = ctypes.c_int
+    lib.fla_sm100_bwd.argtypes = [ctypes.POINTER(FlaArgs)]
+    lib.fla_sm100_last_launch_count.restype = ctypes.c_int
+    if lib.fla_sm100_abi_version() != FLA_ABI_VERSION:
+        raise ImportError("libflashlinear_sm100.so has a different ABI version; rebuild it")
+    _lib = lib
+    return lib
+
+
+def strerror(code: int) -> str:
+    return load().fla_sm100_strerror(code).decode()

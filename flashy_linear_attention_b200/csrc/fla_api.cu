@@ -1,0 +1,440 @@
+// C ABI of libflashlinear_sm100.so (declared in include/flashlinear_sm100.h).
+//
+// Forward and backward of causal linear attention are expressed with ONE device kernel,
+// fla_chunk_kernel (fla_kernel.cuh), which computes  out_i = sum_{j<=i} (a_i . b_j) c_j  (or the
+// anti-causal sum j>=i). With a=q, b=k, c=v this is the forward output
+// (flashlinear/kernels/linear_attn_kernels.py:74-82); the gradients of
+// flashlinear/kernels/linear_attn_kernels.py:179-197 and :291-299 are the same product with
+// permuted operands:
+//     dQ_i = sum_{j<=i} (dO_i . v_j) k_j      causal      (a=dO, b=v,  c=k)
+//     dV_j = sum_{i>=j} (k_j . q_i) dO_i      anti-causal (a=k,  b=q,  c=dO)
+//     dK_j = sum_{i>=j} (v_j . dO_i) q_i      anti-causal (a=v,  b=dO, c=q)
+// dV and dK run side by side in one grid so that their shared reads of q and dO hit in L2.
+#include "../../include/flashlinear_sm100.h"
+#include "fla_kernel.cuh"
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+
+namespace {
+
+using fla::KernelParams;
+using fla::Problem;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static std::atomic<EncodeTiledFn> cached{nullptr};
+  EncodeTiledFn fn = cached.load(std::memory_order_acquire);
+  if (fn) return fn;
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) !=
+          cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess || sym == nullptr) {
+    return nullptr;
+  }
+  fn = reinterpret_cast<EncodeTiledFn>(sym);
+  cached.store(fn, std::memory_order_release);
+  return fn;
+}
+
+thread_local int g_last_launches = 0;
+
+struct Operand {
+  const void* ptr;
+  int64_t sb, sh, sn;  // element strides
+  int dim;             // valid head dim (columns beyond it read as zero / are not written)
+};
+
+Operand operand(const FlaTensor& t, int dim) {
+  Operand o;
+  o.ptr = t.ptr;
+  o.sb = t.stride_b;
+  o.sh = t.stride_h;
+  o.sn = t.stride_n;
+  o.dim = dim;
+  return o;
+}
+
+int check_operand(const Operand& o, int B, int H) {
+  if (o.ptr == nullptr) return FLA_ERR_INVALID;
+  if (reinterpret_cast<uintptr_t>(o.ptr) % 16 != 0) return FLA_ERR_ALIGNMENT;
+  if ((o.sn * 2) % 16 != 0 || o.sn < o.dim) return FLA_ERR_ALIGNMENT;
+  if (H > 1 && (o.sh * 2) % 16 != 0) return FLA_ERR_ALIGNMENT;
+  if (B > 1 && (o.sb * 2) % 16 != 0) return FLA_ERR_ALIGNMENT;
+  return FLA_OK;
+}
+
+// 4-D tensor map (dim, token, head, batch); box = 64 columns x 128 tokens, 128-byte swizzle.
+// Columns >= dim and tokens >= N are out of bounds: loads fill zeros, stores skip them.
+int encode_map(CUtensorMap* m, const Operand& o, int B, int H, int N) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return FLA_ERR_CUDA;
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(o.sn) * 2;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(o.dim), static_cast<cuuint64_t>(N),
+                        static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(B)};
+  // Strides of size-1 dimensions are never used for addressing but must still be valid.
+  cuuint64_t sh = (H > 1) ? static_cast<cuuint64_t>(o.sh) * 2 : row_bytes * N;
+  cuuint64_t sb = (B > 1) ? static_cast<cuuint64_t>(o.sb) * 2 : sh * H;
+  cuuint64_t strides[3] = {row_bytes, sh, sb};
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(fla::kChunk), 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(o.ptr), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FLA_OK : FLA_ERR_CUDA;
+}
+
+// One product out_i = sum (a_i . b_j) c_j; a, b have dim `da`, c and out have dim `dc`.
+struct Product {
+  Operand a, b, c, out;
+  int reverse;
+  const float* ext_init;  // caller's running state, or null
+  float* ext_final;
+  int ext_trans;  // the caller's state arrays hold the transpose of the product's [da][dc] state
+};
+
+// ---------------------------------------------------------------- segment state scan
+// ws: [prob][bh][seg][rows*cols] holds per-segment sums on entry and, on exit, the exclusive
+// prefix (in scan order) including the caller's initial state.
+struct ScanProblem {
+  float* ws;
+  const float* ext_init;
+  float* ext_final;
+  int ext_trans;
+};
+struct ScanParams {
+  ScanProblem prob[3];
+  int nseg, rows, cols, bh_count;
+  int have_last;  // the last segment's sum is present (needed only for ext_final)
+};
+
+__global__ void fla_state_scan_kernel(const ScanParams sp) {
+  const ScanProblem& pr = sp.prob[blockIdx.z];
+  const int bh = blockIdx.y;
+  const int elems = sp.rows * sp.cols;
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= elems) return;
+  const int row = e / sp.cols, col = e % sp.cols;
+  const size_t ext_idx = static_cast<size_t>(bh) * elems +
+                         (pr.ext_trans ? static_cast<size_t>(col) * sp.rows + row : e);
+  float run = pr.ext_init ? pr.ext_init[ext_idx] : 0.f;
+  float* base = pr.ws + static_cast<size_t>(bh) * sp.nseg * elems + e;
+  for (int g = 0; g < sp.nseg; ++g) {
+    float* p = base + static_cast<size_t>(g) * elems;
+    const bool present = (g < sp.nseg - 1) || sp.have_last;
+    const float local = present ? *p : 0.f;
+    *p = run;
+    run += local;
+  }
+  if (pr.ext_final) pr.ext_final[ext_idx] = run;
+}
+
+// ---------------------------------------------------------------- launch plumbing
+struct DeviceInfo {
+  int sm_count;
+  int cc_major;
+  bool attr_set[2];
+};
+
+int device_info(DeviceInfo** out) {
+  static DeviceInfo infos[64];
+  static std::atomic<int> ready[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
+  if (ready[dev].load(std::memory_order_acquire) != 2) {
+    int expected = 0;
+    if (ready[dev].compare_exchange_strong(expected, 1)) {
+      DeviceInfo& d = infos[dev];
+      d.sm_count = 148;
+      d.cc_major = 0;
+      cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+      cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+      bool ok = true;
+      ok &= cudaFuncSetAttribute(fla::fla_chunk_kernel<64, 64>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 fla::Cfg<64, 64>::SMEM_BYTES) == cudaSuccess;
+      ok &= cudaFuncSetAttribute(fla::fla_chunk_kernel<128, 128>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 fla::Cfg<128, 128>::SMEM_BYTES) == cudaSuccess;
+      d.attr_set[0] = d.attr_set[1] = ok;
+      ready[dev].store(2, std::memory_order_release);
+    } else {
+      while (ready[dev].load(std::memory_order_acquire) != 2) {
+      }
+    }
+  }
+  *out = &infos[dev];
+  return FLA_OK;
+}
+
+int pick_template(int da, int dc) {
+  const int m = da > dc ? da : dc;
+  if (m <= 64) return 64;
+  if (m <= 128) return 128;
+  return 0;
+}
+
+int auto_segments(int nprob, int bh, int nchunks, int sm_count) {
+  const long ctas = static_cast<long>(nprob) * bh;
+  if (ctas * 4 >= static_cast<long>(sm_count) * 3) return 1;  // already >= 75 % of the SMs
+  int want = static_cast<int>((2L * sm_count + ctas - 1) / ctas);
+  int max_seg = nchunks / 2;  // at least two chunks per segment
+  if (max_seg < 1) max_seg = 1;
+  if (want > max_seg) want = max_seg;
+  if (want < 1) want = 1;
+  // make segments equal: seg_chunks = ceil(nchunks / want), then recompute the count
+  const int seg_chunks = (nchunks + want - 1) / want;
+  return (nchunks + seg_chunks - 1) / seg_chunks;
+}
+
+size_t segment_ws_bytes(int nprob, int bh, int nseg, int rows, int cols) {
+  if (nseg <= 1) return 0;
+  return static_cast<size_t>(nprob) * bh * nseg * rows * cols * sizeof(float);
+}
+
+template <int D>
+int launch_kernel(const KernelParams& kp, dim3 grid, cudaStream_t stream) {
+  fla::fla_chunk_kernel<D, D><<<grid, fla::kThreads, fla::Cfg<D, D>::SMEM_BYTES, stream>>>(kp);
+  ++g_last_launches;
+  return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
+
+int launch_template(int tmpl, const KernelParams& kp, dim3 grid, cudaStream_t stream) {
+  if (tmpl == 64) return launch_kernel<64>(kp, grid, stream);
+  if (tmpl == 128) return launch_kernel<128>(kp, grid, stream);
+  return FLA_ERR_UNSUPPORTED;
+}
+
+// Runs `nprob` products that share shapes (da, dc) in one grid (plus, with segments, a state pass
+// and a scan before it).
+int run_products(const Product* prods, int nprob, int B, int H, int N, int da, int dc,
+                 int segments, void* workspace, size_t workspace_bytes, int32_t* status,
+                 cudaStream_t stream, const DeviceInfo& dev) {
+  const int tmpl = pick_template(da, dc);
+  if (tmpl == 0) return FLA_ERR_UNSUPPORTED;
+  const int bh = B * H;
+  const int nchunks = (N + fla::kChunk - 1) / fla::kChunk;
+  int nseg = segments;
+  if (nseg <= 0) nseg = auto_segments(nprob, bh, nchunks, dev.sm_count);
+  if (nseg > nchunks) nseg = nchunks;
+  const int seg_chunks = (nchunks + nseg - 1) / nseg;
+  nseg = (nchunks + seg_chunks - 1) / seg_chunks;
+  const size_t ws_per_prob = static_cast<size_t>(bh) * nseg * da * dc;
+  if (nseg > 1) {
+    if (workspace == nullptr || workspace_bytes < segment_ws_bytes(nprob, bh, nseg, da, dc))
+      return FLA_ERR_WORKSPACE;
+  }
+
+  KernelParams kp;
+  memset(&kp, 0, sizeof(kp));
+  kp.heads = H;
+  kp.nchunks = nchunks;
+  kp.seg_chunks = seg_chunks;
+  kp.st_rows = da;
+  kp.st_cols = dc;
+  kp.status = status;
+  bool want_final = false;
+  for (int i = 0; i < nprob; ++i) {
+    const Product& pd = prods[i];
+    int rc;
+    if ((rc = check_operand(pd.a, B, H)) || (rc = check_operand(pd.b, B, H)) ||
+        (rc = check_operand(pd.c, B, H)) || (rc = check_operand(pd.out, B, H)))
+      return rc;
+    Problem& pr = kp.prob[i];
+    if ((rc = encode_map(&pr.q, pd.a, B, H, N)) || (rc = encode_map(&pr.k, pd.b, B, H, N)) ||
+        (rc = encode_map(&pr.v, pd.c, B, H, N)) || (rc = encode_map(&pr.o, pd.out, B, H, N)))
+      return rc;
+    pr.reverse = pd.reverse;
+    want_final |= (pd.ext_final != nullptr);
+  }
+
+  if (nseg == 1) {
+    for (int i = 0; i < nprob; ++i) {
+      kp.prob[i].s_init = prods[i].ext_init;
+      kp.prob[i].s_final = prods[i].ext_final;
+      kp.prob[i].st_trans = prods[i].ext_trans;
+    }
+    kp.mode = 0;
+    return launch_template(tmpl, kp, dim3(nprob, 1, bh), stream);
+  }
+
+  // Pass A: per-segment sums of b^T c into the workspace (the last segment only when a final
+  // state is wanted), exclusive scan over segments, then pass B with per-segment initial states.
+  float* ws = static_cast<float*>(workspace);
+  ScanParams sp;
+  memset(&sp, 0, sizeof(sp));
+  for (int i = 0; i < nprob; ++i) {
+    kp.prob[i].s_init = nullptr;
+    kp.prob[i].s_final = ws + i * ws_per_prob;
+    kp.prob[i].st_trans = 0;
+    sp.prob[i].ws = ws + i * ws_per_prob;
+    sp.prob[i].ext_init = prods[i].ext_init;
+    sp.prob[i].ext_final = prods[i].ext_final;
+    sp.prob[i].ext_trans = prods[i].ext_trans;
+  }
+  kp.mode = 1;
+  kp.skip_last_segment = want_final ? 0 : 1;
+  int rc = launch_template(tmpl, kp, dim3(nprob, nseg, bh), stream);
+  if (rc) return rc;
+  sp.nseg = nseg;
+  sp.rows = da;
+  sp.cols = dc;
+  sp.bh_count = bh;
+  sp.have_last = want_final ? 1 : 0;
+  {
+    const int elems = da * dc;
+    dim3 grid((elems + 255) / 256, bh, nprob);
+    fla_state_scan_kernel<<<grid, 256, 0, stream>>>(sp);
+    ++g_last_launches;
+    if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
+  }
+  for (int i = 0; i < nprob; ++i) {
+    kp.prob[i].s_init = ws + i * ws_per_prob;
+    kp.prob[i].s_final = nullptr;
+  }
+  kp.mode = 0;
+  kp.skip_last_segment = 0;
+  return launch_template(tmpl, kp, dim3(nprob, nseg, bh), stream);
+}
+
+int check_common(const FlaArgs* a, DeviceInfo** dev) {
+  if (a == nullptr) return FLA_ERR_INVALID;
+  if (a->batch <= 0 || a->heads <= 0 || a->seqlen <= 0 || a->dk <= 0 || a->dv <= 0)
+    return FLA_ERR_INVALID;
+  if (static_cast<long>(a->batch) * a->heads > 65535) return FLA_ERR_UNSUPPORTED;
+  int rc = device_info(dev);
+  if (rc) return rc;
+  if ((*dev)->cc_major != 10) return FLA_ERR_DEVICE;
+  if (!(*dev)->attr_set[0]) return FLA_ERR_CUDA;
+  return FLA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fla_sm100_abi_version(void) { return FLA_ABI_VERSION; }
+
+const char* fla_sm100_strerror(int code) {
+  switch (code) {
+    case FLA_OK: return "ok";
+    case FLA_ERR_INVALID: return "invalid argument (null pointer or non-positive size)";
+    case FLA_ERR_UNSUPPORTED: return "unsupported head dimension or batch*heads for the sm_100a kernels";
+    case FLA_ERR_ALIGNMENT: return "pointer or byte stride is not a multiple of 16";
+    case FLA_ERR_CUDA: return "a CUDA call failed";
+    case FLA_ERR_WORKSPACE: return "workspace missing or too small";
+    case FLA_ERR_DEVICE: return "current device is not an sm_100 GPU";
+    default: return "unknown error";
+  }
+}
+
+int fla_sm100_last_launch_count(void) { return g_last_launches; }
+
+int fla_sm100_auto_segments(const FlaArgs* a, int pass) {
+  if (a == nullptr) return 1;
+  if (a->segments > 0) return a->segments;
+  int sm = 148;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess)
+    cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev);
+  const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
+  return auto_segments(pass == 0 ? 1 : 3, a->batch * a->heads, nchunks, sm);
+}
+
+size_t fla_sm100_workspace_bytes(const FlaArgs* a, int pass) {
+  if (a == nullptr) return 0;
+  const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
+  int nseg = fla_sm100_auto_segments(a, pass);
+  if (nseg > nchunks) nseg = nchunks;
+  if (nseg <= 1) return 0;
+  const int seg_chunks = (nchunks + nseg - 1) / nseg;
+  nseg = (nchunks + seg_chunks - 1) / seg_chunks;
+  return segment_ws_bytes(pass == 0 ? 1 : 3, a->batch * a->heads, nseg, a->dk, a->dv) + 1024;
+}
+
+int fla_sm100_fwd(const FlaArgs* a) {
+  DeviceInfo* dev = nullptr;
+  g_last_launches = 0;
+  int rc = check_common(a, &dev);
+  if (rc) return rc;
+  Product p;
+  p.a = operand(a->q, a->dk);
+  p.b = operand(a->k, a->dk);
+  p.c = operand(a->v, a->dv);
+  p.out = operand(a->o, a->dv);
+  p.reverse = 0;
+  p.ext_init = a->s_init;
+  p.ext_final = a->s_final;
+  p.ext_trans = 0;
+  return run_products(&p, 1, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->segments,
+                      a->workspace, a->workspace_bytes, a->status,
+                      static_cast<cudaStream_t>(a->stream), *dev);
+}
+
+int fla_sm100_bwd(const FlaArgs* a) {
+  DeviceInfo* dev = nullptr;
+  g_last_launches = 0;
+  int rc = check_common(a, &dev);
+  if (rc) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  // dQ: causal, state sum v^T k = S^T (dv x dk)
+  Product pq;
+  pq.a = operand(a->d_o, a->dv);
+  pq.b = operand(a->v, a->dv);
+  pq.c = operand(a->k, a->dk);
+  pq.out = operand(a->d_q, a->dk);
+  pq.reverse = 0;
+  pq.ext_init = a->s_init;
+  pq.ext_final = nullptr;
+  pq.ext_trans = 1;
+  // dV: anti-causal, state sum q^T dO = R (dk x dv)
+  Product pv;
+  pv.a = operand(a->k, a->dk);
+  pv.b = operand(a->q, a->dk);
+  pv.c = operand(a->d_o, a->dv);
+  pv.out = operand(a->d_v, a->dv);
+  pv.reverse = 1;
+  pv.ext_init = a->r_init;
+  pv.ext_final = a->r_final;
+  pv.ext_trans = 0;
+  // dK: anti-causal, state sum dO^T q = R^T (dv x dk)
+  Product pk;
+  pk.a = operand(a->v, a->dv);
+  pk.b = operand(a->d_o, a->dv);
+  pk.c = operand(a->q, a->dk);
+  pk.out = operand(a->d_k, a->dk);
+  pk.reverse = 1;
+  pk.ext_init = a->r_init;
+  pk.ext_final = nullptr;
+  pk.ext_trans = 1;
+
+  const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
+  int nseg = a->segments > 0 ? a->segments
+                             : auto_segments(3, a->batch * a->heads, nchunks, dev->sm_count);
+  if (a->dk == a->dv) {
+    // Same shapes: one grid. Block x = product; dV and dK of a head are neighbours in launch order.
+    Product all[3] = {pq, pv, pk};
+    return run_products(all, 3, a->batch, a->heads, a->seqlen, a->dk, a->dv, nseg, a->workspace,
+                        a->workspace_bytes, a->status, stream, *dev);
+  }
+  // dk != dv: dQ and dK have (da, dc) = (dv, dk); dV has (dk, dv). The caller's scratch is split
+  // two thirds / one third.
+  Product two[2] = {pq, pk};
+  const size_t third = (a->workspace_bytes / 3) & ~static_cast<size_t>(255);
+  char* ws = static_cast<char*>(a->workspace);
+  rc = run_products(two, 2, a->batch, a->heads, a->seqlen, a->dv, a->dk, nseg, ws,
+                    ws ? 2 * third : 0, a->status, stream, *dev);
+  if (rc) return rc;
+  return run_products(&pv, 1, a->batch, a->heads, a->seqlen, a->dk, a->dv, nseg,
+                      ws ? ws + 2 * third : nullptr, ws ? third : 0, a->status, stream, *dev);
+}
+
+}  // extern "C"

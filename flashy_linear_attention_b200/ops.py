@@ -1,0 +1,255 @@
+"""Launch wrappers with the names, arguments and error behaviour of the reference's
+``flashlinear.kernels`` module (flashlinear/kernels/linear_attn_kernels.py:310-384 and
+flashlinear/kernels/linear_attn_kernels_smallv_hd.py:320-405), calling the sm_100a kernels of
+libflashlinear_sm100.so through its C ABI instead of Triton.
+
+All four wrappers return the *unnormalised* causal product ``(Q K^T (.) M) V`` (or its gradients);
+the denominator stays in PyTorch, as in the reference (README.md:22-30).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import FlaArgs, FlaTensor
+
+MAX_HEAD_DIM = 128  # largest head dim the kernels are built for
+
+_status_words = {}
+
+
+def _next_pow2(x: int) -> int:
+    return 1 << (max(int(x), 1) - 1).bit_length()
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    w = _status_words.get(key)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+        _status_words[key] = w
+    return w
+
+
+def check_status(device=None) -> None:
+    """Synchronises and raises RuntimeError if a kernel on `device` gave up on a bounded wait."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    w = _status_word(dev)
+    val = int(w.item())
+    if val != 0:
+        w.zero_()
+        raise RuntimeError(
+            f"flashlinear sm_100a kernel reported status {val}: a device-side wait timed out; "
+            "results of the affected call are invalid"
+        )
+
+
+def _check_inputs(*tensors: torch.Tensor) -> None:
+    dev = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError(
+                "flashlinear: tensors must be CUDA tensors on an sm_100 GPU (no CPU fallback exists)"
+            )
+        if t.device != dev:
+            raise RuntimeError("flashlinear: all tensors must be on the same device")
+        if t.dtype != torch.bfloat16:
+            raise TypeError(
+                f"flashlinear: expected torch.bfloat16 tensors, got {t.dtype} "
+                "(use torch.autocast or cast the inputs)"
+            )
+        if t.dim() != 4:
+            raise ValueError("flashlinear: expected [batch, heads, seq, head_dim] tensors")
+
+
+def _kernel_view(t: torch.Tensor) -> torch.Tensor:
+    """Returns `t` if the kernels can read it in place (unit innermost stride, 16-byte aligned
+    base and row/head/batch strides), else a repacked copy whose rows are padded to 8 elements."""
+    d = t.shape[-1]
+    ok = t.stride(3) == 1 and t.data_ptr() % 16 == 0 and t.stride(2) >= d
+    for dim in (0, 1, 2):
+        if t.shape[dim] > 1 and t.stride(dim) % 8 != 0:
+            ok = False
+    if ok:
+        return t
+    dpad = (d + 7) // 8 * 8
+    buf = torch.empty(t.shape[:-1] + (dpad,), dtype=t.dtype, device=t.device)
+    view = buf[..., :d]
+    view.copy_(t)
+    return view
+
+
+def _out_like(t: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Output with the layout of ``torch.empty_like(t)`` plus the view the kernel writes to
+    (a padded scratch tensor when empty_like's layout is not addressable by the kernels)."""
+    out = torch.empty_like(t)
+    kv = _kernel_view_for_output(out)
+    return out, kv
+
+
+def _kernel_view_for_output(out: torch.Tensor) -> torch.Tensor:
+    d = out.shape[-1]
+    ok = out.stride(3) == 1 and out.data_ptr() % 16 == 0 and out.stride(2) >= d
+    for dim in (0, 1, 2):
+        if out.shape[dim] > 1 and out.stride(dim) % 8 != 0:
+            ok = False
+    if ok:
+        return out
+    dpad = (d + 7) // 8 * 8
+    buf = torch.empty(out.shape[:-1] + (dpad,), dtype=out.dtype, device=out.device)
+    return buf[..., :d]
+
+
+def _desc(t: Optional[torch.Tensor]) -> FlaTensor:
+    if t is None:
+        return FlaTensor(None, 0, 0, 0)
+    return FlaTensor(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
+
+
+def _fptr(t: Optional[torch.Tensor], name: str, shape) -> Optional[int]:
+    if t is None:
+        return None
+    if t.dtype != torch.float32 or not t.is_contiguous() or tuple(t.shape) != tuple(shape):
+        raise ValueError(f"flashlinear: {name} must be a contiguous float32 tensor of shape {tuple(shape)}")
+    return t.data_ptr()
+
+
+def _call(pass_id: int, args: FlaArgs, device: torch.device) -> None:
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        args.stream = torch.cuda.current_stream(device).cuda_stream
+        args.status = _status_word(device).data_ptr()
+        need = lib.fla_sm100_workspace_bytes(ctypes.byref(args), pass_id)
+        ws = None
+        if need > 0:
+            ws = torch.empty(need, dtype=torch.uint8, device=device)
+            args.workspace = ws.data_ptr()
+            args.workspace_bytes = need
+        fn = lib.fla_sm100_fwd if pass_id == 0 else lib.fla_sm100_bwd
+        rc = fn(ctypes.byref(args))
+    if rc != 0:
+        raise RuntimeError(f"flashlinear: libflashlinear_sm100 returned {rc}: {_lib.strerror(rc)}")
+    if os.environ.get("FLA_DEBUG", "0") == "1":
+        check_status(device)
+
+
+def causal_dot_product_fwd(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    s_init: Optional[torch.Tensor] = None,
+    s_final: Optional[torch.Tensor] = None,
+    segments: int = 0,
+) -> torch.Tensor:
+    """out[b,h,i] = sum_{j<=i} (q_i . k_j) v_j, bf16 in / bf16 out, fp32 accumulation.
+
+    s_init / s_final are optional fp32 [batch*heads, dk, dv] running states (sum of k_j^T v_j
+    before / after this call's tokens) for sequence-sharded or resumed calls.
+    """
+    _check_inputs(q, k, v)
+    B, H, N, dk = q.shape
+    dv = v.shape[-1]
+    qv, kv_, vv = _kernel_view(q), _kernel_view(k), _kernel_view(v)
+    out, ov = _out_like(v)
+    a = FlaArgs()
+    a.batch, a.heads, a.seqlen, a.dk, a.dv = B, H, N, dk, dv
+    a.q, a.k, a.v, a.o = _desc(qv), _desc(kv_), _desc(vv), _desc(ov)
+    a.s_init = _fptr(s_init, "s_init", (B * H, dk, dv))
+    a.s_final = _fptr(s_final, "s_final", (B * H, dk, dv))
+    a.segments = segments
+    _call(0, a, q.device)
+    if ov is not out:
+        out.copy_(ov)
+    return out
+
+
+def causal_dot_product_bwd(
+    grad_output: torch.Tensor,
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    s_init: Optional[torch.Tensor] = None,
+    r_init: Optional[torch.Tensor] = None,
+    r_final: Optional[torch.Tensor] = None,
+    segments: int = 0,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gradients (dQ, dK, dV) of causal_dot_product_fwd for upstream gradient `grad_output`."""
+    _check_inputs(grad_output, q, k, v)
+    B, H, N, dk = q.shape
+    dv = v.shape[-1]
+    gv, qv, kv_, vv = (_kernel_view(t) for t in (grad_output, q, k, v))
+    dQ, dQv = _out_like(q)
+    dK, dKv = _out_like(k)
+    dV, dVv = _out_like(v)
+    a = FlaArgs()
+    a.batch, a.heads, a.seqlen, a.dk, a.dv = B, H, N, dk, dv
+    a.q, a.k, a.v, a.d_o = _desc(qv), _desc(kv_), _desc(vv), _desc(gv)
+    a.d_q, a.d_k, a.d_v = _desc(dQv), _desc(dKv), _desc(dVv)
+    a.s_init = _fptr(s_init, "s_init", (B * H, dk, dv))
+    a.r_init = _fptr(r_init, "r_init", (B * H, dk, dv))
+    a.r_final = _fptr(r_final, "r_final", (B * H, dk, dv))
+    a.segments = segments
+    _call(1, a, q.device)
+    for full, view in ((dQ, dQv), (dK, dKv), (dV, dVv)):
+        if view is not full:
+            full.copy_(view)
+    return dQ, dK, dV
+
+
+# ------------------------------------------------------------------------------------------------
+# The reference's four wrapper names.
+# ------------------------------------------------------------------------------------------------
+
+
+def _assert_shapes(hd_qk: int, sq: int) -> None:
+    # Same preconditions (and AssertionError) as the reference wrappers, with the head-dim cap of
+    # the kernels built here (linear_attn_kernels.py:322-325 asserts hd <= 256).
+    block_sq = 64 if _next_pow2(hd_qk) <= 128 else 32
+    assert hd_qk <= MAX_HEAD_DIM, f"Only head_dims <= {MAX_HEAD_DIM} are supported."
+    assert (
+        sq % block_sq == 0
+    ), f"Number of elements in sequence must be a multiple of {block_sq}, {sq, block_sq}"
+
+
+def linear_flash_wrapper_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """Causal linear attention forward, dk == dv (linear_attn_kernels.py:310-341)."""
+    batch, nh, sq, hd = q.shape
+    _assert_shapes(hd, sq)
+    return causal_dot_product_fwd(q, k, v)
+
+
+def linear_flash_wrapper_bwd(
+    grad_output: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Causal linear attention backward, dk == dv (linear_attn_kernels.py:345-384)."""
+    batch, nh, sq, hd = q.shape
+    _assert_shapes(hd, sq)
+    return causal_dot_product_bwd(grad_output, q, k, v)
+
+
+def linear_flash_wrapper_fwd_smallv_hd(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
+) -> torch.Tensor:
+    """Forward with separate q/k and v head dims (linear_attn_kernels_smallv_hd.py:320-359)."""
+    batch, nh, sq, hd_qk = q.shape
+    hd_v = v.shape[-1]
+    assert _next_pow2(hd_v) == hd_v, "Expected value head dimension to be a power of 2."
+    assert _next_pow2(hd_v) <= _next_pow2(
+        hd_qk
+    ), "Value head dimension must be less than Query/Key head dimension."
+    _assert_shapes(hd_qk, sq)
+    return causal_dot_product_fwd(q, k, v)
+
+
+def linear_flash_wrapper_bwd_smallv_hd(
+    grad_output: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Backward with separate q/k and v head dims (linear_attn_kernels_smallv_hd.py:363-405)."""
+    batch, nh, sq, hd_qk = q.shape
+    assert hd_qk <= MAX_HEAD_DIM, f"Only head_dims <= {MAX_HEAD_DIM} are supported."
+    assert sq % 64 == 0, "Number of elements in sequence must be a multiple of 64"
+    return causal_dot_product_bwd(grad_output, q, k, v)

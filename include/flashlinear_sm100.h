@@ -1,0 +1,107 @@
+/*
+ * C ABI of libflashlinear_sm100.so: causal, unnormalised linear attention
+ *     O = (Q K^T (.) M) V          (M = lower-triangular ones, diagonal included)
+ * forward and backward on NVIDIA B200 (sm_100a), bf16 operands, fp32 accumulation.
+ *
+ * These entry points are what the launch wrappers of the reference library
+ * (flashlinear/kernels/linear_attn_kernels.py:310-341 `linear_flash_wrapper_fwd`,
+ *  :345-384 `linear_flash_wrapper_bwd`, and
+ *  flashlinear/kernels/linear_attn_kernels_smallv_hd.py:320-359 / :363-405, the
+ *  `_smallv_hd` pair for dk != dv) bind instead of launching their Triton kernels.
+ *
+ * Conventions
+ *  - plain C types only; all tensor pointers are device pointers on the CURRENT device;
+ *  - tensors are [batch, heads, seqlen, dim] bf16 with arbitrary (batch, head, token) element
+ *    strides and an innermost stride of 1; base addresses and byte strides must be multiples
+ *    of 16 (return FLA_ERR_ALIGNMENT otherwise; the Python wrapper then repacks);
+ *  - every call is asynchronous on `stream`, never synchronises, never allocates or frees
+ *    device memory; scratch memory (when fla_sm100_workspace_bytes() > 0) is the caller's;
+ *  - returns 0 or a negative FLA_ERR_* code for argument errors, synchronously;
+ *  - device-side waits are bounded; a wait that runs out sets bit 0 of *status (optional device
+ *    word the caller zero-initialises and reads after synchronising).
+ */
+#ifndef FLASHLINEAR_SM100_H_
+#define FLASHLINEAR_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FLA_ABI_VERSION 1
+
+enum {
+  FLA_OK = 0,
+  FLA_ERR_INVALID = -1,     /* null pointer, non-positive size, bad struct */
+  FLA_ERR_UNSUPPORTED = -2, /* head dims outside what the kernels are built for */
+  FLA_ERR_ALIGNMENT = -3,   /* pointer or byte stride not a multiple of 16 */
+  FLA_ERR_CUDA = -4,        /* a CUDA runtime / driver call failed */
+  FLA_ERR_WORKSPACE = -5,   /* workspace missing or too small */
+  FLA_ERR_DEVICE = -6       /* current device is not compute capability 10.x */
+};
+
+/* One [batch, heads, seqlen, dim] bf16 tensor: device pointer and element strides of the three
+ * outer dimensions (the innermost stride is 1). */
+typedef struct FlaTensor {
+  void* ptr;
+  int64_t stride_b;
+  int64_t stride_h;
+  int64_t stride_n;
+} FlaTensor;
+
+typedef struct FlaArgs {
+  int32_t batch, heads, seqlen;
+  int32_t dk; /* head dim of q, k (and dQ, dK) */
+  int32_t dv; /* head dim of v, o (and dO, dV) */
+
+  FlaTensor q, k, v; /* inputs of both passes */
+  FlaTensor o;       /* forward output          [.., dv] */
+  FlaTensor d_o;     /* backward input          [.., dv] */
+  FlaTensor d_q;     /* backward outputs        [.., dk] */
+  FlaTensor d_k;     /*                         [.., dk] */
+  FlaTensor d_v;     /*                         [.., dv] */
+
+  /* Optional running state, fp32 [batch*heads, dk, dv], contiguous. Forward: s_init is
+   * S = sum_j k_j^T v_j over the tokens that precede this call's tokens, s_final receives the
+   * state after them. Backward: s_init as in the forward (needed for dQ), r_init is
+   * R = sum_i q_i^T dO_i over the tokens that FOLLOW this call's tokens, r_final receives the
+   * state including them. NULL = zero / not wanted. */
+  const float* s_init;
+  float* s_final;
+  const float* r_init;
+  float* r_final;
+
+  /* Sequence segments per head (intra-GPU sequence split). 0 = pick automatically, 1 = none.
+   * With more than one segment the call needs fla_sm100_workspace_bytes() of scratch. */
+  int32_t segments;
+
+  void* workspace;
+  size_t workspace_bytes;
+
+  int32_t* status; /* optional device word, see above */
+  void* stream;    /* cudaStream_t */
+} FlaArgs;
+
+/* pass: 0 = forward, 1 = backward */
+int fla_sm100_abi_version(void);
+const char* fla_sm100_strerror(int code);
+size_t fla_sm100_workspace_bytes(const FlaArgs* args, int pass);
+/* Number of segments the call will use for args->segments == 0. */
+int fla_sm100_auto_segments(const FlaArgs* args, int pass);
+
+/* replaces linear_flash_wrapper_fwd / linear_flash_wrapper_fwd_smallv_hd
+ * (flashlinear/kernels/linear_attn_kernels.py:310, linear_attn_kernels_smallv_hd.py:320) */
+int fla_sm100_fwd(const FlaArgs* args);
+/* replaces linear_flash_wrapper_bwd / linear_flash_wrapper_bwd_smallv_hd
+ * (flashlinear/kernels/linear_attn_kernels.py:345, linear_attn_kernels_smallv_hd.py:363) */
+int fla_sm100_bwd(const FlaArgs* args);
+
+/* Number of kernels the last fwd / bwd call on this thread launched (for benchmarks). */
+int fla_sm100_last_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHLINEAR_SM100_H_ */
