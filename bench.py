@@ -1,0 +1,346 @@
+"""Benchmark of the causal linear attention hot path (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload cfg3]
+
+One "step" = one forward + one backward of `LinearAttention` over the whole workload.
+Headline workload (cfg3): bf16, B=4, H=32, N=8192, dk=dv=128; q, k = elu(N(0,1)) + 1,
+v, dO ~ N(0,1), seeded synthetic data. Metric: Mtokens/s = B*N / step time, whole job.
+
+At N > 1 (launched by torch.distributed.run, one rank per GPU) the batch*heads independent heads
+of the SAME workload are split over the ranks (strong scaling; no data-path collective), timing is
+barrier + max over ranks. Prints one JSON line on rank 0.
+
+`--impl reference` times the reference's naive PyTorch path (restated in oracle/torch_naive.py) on
+the host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (B, H, N, dk, dv)
+    "cfg2": (8, 16, 4096, 64, 64),
+    "cfg3": (4, 32, 8192, 128, 128),
+    "cfg5": (1, 32, 65536, 128, 128),
+}
+METRIC = "fwd+bwd Mtokens/s, N=8K D=128 bf16, 1/2/4/8 B200; % tensor/HBM roofline"
+UNIT = "Mtokens/s"
+
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the forward and backward launches
+# of fla_chunk_kernel<128,128> at cfg3, from the ncu capture summarised under profiles/.
+# None until such a capture exists for the current kernel.
+NCU_TRAFFIC_BYTES_PER_STEP = {"cfg3": None}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    except Exception:
+        return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def algorithmic_bytes(B, H, N, dk, dv):
+    """Compulsory HBM bytes per step, bf16: fwd reads q,k,v and writes o; bwd reads q,k,v,dO and
+    writes dQ,dK,dV."""
+    th = B * H * N
+    fwd = th * (2 * dk + 2 * dv) * 2
+    bwd = th * ((2 * dk + 2 * dv) + (2 * dk + dv)) * 2
+    return fwd, bwd
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "50", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.thread.join(timeout=2)
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nme, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(nme)
+        return {
+            "sm_mhz": statistics.median(sm) if sm else None,
+            "sm_max_mhz": max(smax) if smax else None,
+            "samples": len(sm),
+            "reasons": sorted(reasons),
+        }
+
+
+def make_inputs(B, H, N, dk, dv, device, seed=0):
+    gen = torch.Generator(device=device).manual_seed(seed)
+    q = (torch.nn.functional.elu(torch.randn(B, H, N, dk, device=device, generator=gen)) + 1).to(torch.bfloat16)
+    k = (torch.nn.functional.elu(torch.randn(B, H, N, dk, device=device, generator=gen)) + 1).to(torch.bfloat16)
+    v = torch.randn(B, H, N, dv, device=device, generator=gen).to(torch.bfloat16)
+    dy = torch.randn(B, H, N, dv, device=device, generator=gen).to(torch.bfloat16)
+    return q, k, v, dy
+
+
+def cpu_baseline_sample(B, H, N, dk, dv, budget_s=15.0, max_heads=8):
+    """Times the naive PyTorch path (oracle port) on the host on a bounded sample: whole heads of
+    one batch entry at the full sequence length. Returns the cpu_baseline dict."""
+    from oracle import torch_naive
+
+    threads = os.cpu_count() or 1
+    t1, used = torch_naive.time_fwd_bwd_cpu(1, 1, N, dk, dv, steps=1, warmup=0, threads=threads)
+    heads = int(max(1, min(max_heads, budget_s // max(t1, 1e-3))))
+    if heads > 1:
+        t, used = torch_naive.time_fwd_bwd_cpu(1, heads, N, dk, dv, steps=1, warmup=0, threads=threads)
+    else:
+        t = t1
+    tokens_equiv = N * heads / H  # a token counts once all H heads of it are done
+    return {
+        "value": tokens_equiv / t / 1e6,
+        "unit": UNIT,
+        "cores": used,
+        "kind": "port",
+        "sample": f"{heads} of {B * H} heads at full N={N}, fp32 fwd+autograd bwd, {t:.2f} s; "
+                  f"scaled to tokens by heads/{H}",
+        "seconds": t,
+    }
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    B, H, N, dk, dv = WORKLOADS[args.workload]
+    from oracle import torch_naive
+
+    threads = os.cpu_count() or 1
+    heads = 1
+    total = args.warmup + args.steps
+    t_probe, used = torch_naive.time_fwd_bwd_cpu(1, heads, N, dk, dv, steps=1, threads=threads)
+    # keep the whole run within a few minutes
+    if t_probe * total > 150:
+        steps, warmup = max(1, int(150 // t_probe) - 1), 1
+    else:
+        steps, warmup = args.steps, args.warmup
+    t, used = torch_naive.time_fwd_bwd_cpu(1, heads, N, dk, dv, steps=steps, warmup=warmup, threads=threads)
+    value = (N * heads / H) / t / 1e6
+    sample = f"{heads} of {B * H} heads at full N={N} per step, fp32 fwd+autograd bwd on {used} host threads"
+    line = {
+        "impl": "reference",
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": t * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: B={B} H={H} N={N} dk={dk} dv={dv}",
+                   "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": used, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the sm_100a kernels have no CPU fallback")
+    import torch.distributed as dist
+
+    from flashlinear import LinearAttention
+    from flashy_linear_attention_b200 import _lib, ops
+    from flashy_linear_attention_b200.sharding import shard_batch_heads
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lib = _lib.load()
+
+    B, H, N, dk, dv = WORKLOADS[args.workload]
+    q, k, v, dy = make_inputs(B, H, N, dk, dv, device)
+    if world > 1:
+        q, k, v, dy = (shard_batch_heads(t, rank, world).contiguous() for t in (q, k, v, dy))
+    Bl, Hl = q.shape[0], q.shape[1]
+    torch.cuda.empty_cache()
+    warmup = max(args.warmup, 3)
+    steps = args.steps
+    stream = torch.cuda.current_stream(device)
+
+    def barrier():
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(device)
+
+    # ---------------------------------------------------------------- kernel-level timing
+    launches = 0
+    for _ in range(warmup):
+        ops.causal_dot_product_fwd(q, k, v)
+        launches_f = lib.fla_sm100_last_launch_count()
+        ops.causal_dot_product_bwd(dy, q, k, v)
+        launches_b = lib.fla_sm100_last_launch_count()
+    barrier()
+    ops.check_status(device)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    for i in range(steps):
+        ev[i][0].record(stream)
+        ops.causal_dot_product_fwd(q, k, v)
+        ev[i][1].record(stream)
+        ops.causal_dot_product_bwd(dy, q, k, v)
+        ev[i][2].record(stream)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ops.check_status(device)
+    total_ms = ev[0][0].elapsed_time(ev[-1][2])
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / steps
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / steps
+    launches = (launches_f + launches_b) * steps
+    t = torch.tensor([total_ms, fwd_ms, bwd_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, fwd_ms, bwd_ms = (float(x) for x in t.tolist())
+    ms_per_step = total_ms / steps
+    value = B * N / (ms_per_step * 1e-3) / 1e6
+
+    # ---------------------------------------------------------------- end to end, host buffers
+    e2e_steps = max(1, min(args.e2e_steps, steps))
+    host_in = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True).copy_(x) for x in (q, k, v, dy)]
+    host_out = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in (v, q, k, v)]
+    h2d = sum(x.numel() * x.element_size() for x in host_in)
+    d2h = sum(x.numel() * x.element_size() for x in host_out)
+
+    def e2e_step():
+        dq_, dk_, dv_, ddy = (x.to(device, non_blocking=True) for x in host_in)
+        dq_.requires_grad_(True); dk_.requires_grad_(True); dv_.requires_grad_(True)
+        out = LinearAttention.apply(dq_, dk_, dv_)
+        grads = torch.autograd.grad(out, (dq_, dk_, dv_), ddy)
+        for dst, src in zip(host_out, (out,) + tuple(grads)):
+            dst.copy_(src.detach(), non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    e2e_ms = torch.tensor([e0.elapsed_time(e1) / e2e_steps], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_value = B * N / (float(e2e_ms.item()) * 1e-3) / 1e6
+    h2d_total = torch.tensor([h2d, d2h], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(h2d_total, op=dist.ReduceOp.SUM)
+    h2d_all, d2h_all = (int(x) for x in h2d_total.tolist())
+
+    if rank == 0:
+        peak, peak_src = measured_peaks()
+        fwd_b, bwd_b = algorithmic_bytes(Bl, Hl, N, dk, dv)  # this rank's share
+        achieved = (fwd_b + bwd_b) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9
+        traffic = NCU_TRAFFIC_BYTES_PER_STEP.get(args.workload) if world == 1 else None
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {
+                "workload": f"{args.workload}: LinearAttention fwd+bwd B={B} H={H} N={N} dk={dk} dv={dv}, "
+                            f"q,k=elu(N(0,1))+1, v,dO~N(0,1), seed 0",
+                "parallelism": f"batch*head sharded over {world} GPU(s): {Bl}x{Hl} heads per GPU, no collective",
+                "l2": f"per-GPU working set {8 * q.numel() * 2 / 1e6:.0f} MB exceeds the 126 MB L2; no flush between steps",
+                "chunk": 128,
+            },
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_all,
+                    "d2h_bytes_per_step": d2h_all, "steps": e2e_steps,
+                    "api": "flashlinear.LinearAttention.apply + torch.autograd.grad, pinned host buffers"},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {
+                "bound": "hbm", "kernel": f"fla_chunk_kernel<{max(dk, dv)},{max(dk, dv)}> (fwd launch + bwd launch)",
+                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "peak_source": peak_src,
+                "algorithmic_bytes_per_step": fwd_b + bwd_b,
+                "traffic": traffic,
+                "fwd": {"ms": fwd_ms, "GBps": fwd_b / (fwd_ms * 1e-3) / 1e9, "frac": fwd_b / (fwd_ms * 1e-3) / 1e9 / peak},
+                "bwd": {"ms": bwd_ms, "GBps": bwd_b / (bwd_ms * 1e-3) / 1e9, "frac": bwd_b / (bwd_ms * 1e-3) / 1e9 / peak},
+            },
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline_sample(B, H, N, dk, dv)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

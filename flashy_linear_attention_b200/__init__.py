@@ -12,6 +12,7 @@ from .ops import (
     causal_dot_product_bwd,
     causal_dot_product_fwd,
     check_status,
+    chunk_state,
     linear_flash_wrapper_bwd,
     linear_flash_wrapper_bwd_smallv_hd,
     linear_flash_wrapper_fwd,
@@ -28,4 +29,5 @@ __all__ = [
     "causal_dot_product_fwd",
     "causal_dot_product_bwd",
     "check_status",
+    "chunk_state",
 ]

@@ -57,6 +57,7 @@ EXPORTED_SYMBOLS = (
     "fla_sm100_auto_segments",
     "fla_sm100_fwd",
     "fla_sm100_bwd",
+    "fla_sm100_state",
     "fla_sm100_last_launch_count",
 )
 
@@ -85,6 +86,8 @@ def load() -> ctypes.CDLL:
     lib.fla_sm100_fwd.argtypes = [ctypes.POINTER(FlaArgs)]
     lib.fla_sm100_bwd.restype = ctypes.c_int
     lib.fla_sm100_bwd.argtypes = [ctypes.POINTER(FlaArgs)]
+    lib.fla_sm100_state.restype = ctypes.c_int
+    lib.fla_sm100_state.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_int]
     lib.fla_sm100_last_launch_count.restype = ctypes.c_int
     if lib.fla_sm100_abi_version() != FLA_ABI_VERSION:
         raise ImportError("libflashlinear_sm100.so has a different ABI version; rebuild it")

@@ -305,6 +305,55 @@ int run_products(const Product* prods, int nprob, int B, int H, int N, int da, i
   return launch_template(tmpl, kp, dim3(nprob, nseg, bh), stream);
 }
 
+// Sum over all tokens of b^T c (fp32, [bh][da][dc]) into `final`: the per-shard state that
+// sequence-sharded callers exchange between GPUs. Uses segments to fill the GPU when bh is small.
+int run_state(const Operand& bop, const Operand& cop, int B, int H, int N, int da, int dc,
+              int segments, float* final, void* workspace, size_t workspace_bytes,
+              int32_t* status, cudaStream_t stream, const DeviceInfo& dev) {
+  const int tmpl = pick_template(da, dc);
+  if (tmpl == 0) return FLA_ERR_UNSUPPORTED;
+  if (final == nullptr) return FLA_ERR_INVALID;
+  const int bh = B * H;
+  const int nchunks = (N + fla::kChunk - 1) / fla::kChunk;
+  int nseg = segments;
+  if (nseg <= 0) nseg = auto_segments(1, bh, nchunks, dev.sm_count);
+  if (nseg > nchunks) nseg = nchunks;
+  const int seg_chunks = (nchunks + nseg - 1) / nseg;
+  nseg = (nchunks + seg_chunks - 1) / seg_chunks;
+  if (nseg > 1 &&
+      (workspace == nullptr || workspace_bytes < segment_ws_bytes(1, bh, nseg, da, dc)))
+    return FLA_ERR_WORKSPACE;
+  int rc;
+  if ((rc = check_operand(bop, B, H)) || (rc = check_operand(cop, B, H))) return rc;
+  KernelParams kp;
+  memset(&kp, 0, sizeof(kp));
+  kp.heads = H;
+  kp.nchunks = nchunks;
+  kp.seg_chunks = seg_chunks;
+  kp.st_rows = da;
+  kp.st_cols = dc;
+  kp.status = status;
+  kp.mode = 1;
+  if ((rc = encode_map(&kp.prob[0].k, bop, B, H, N)) || (rc = encode_map(&kp.prob[0].v, cop, B, H, N)))
+    return rc;
+  kp.prob[0].s_final = (nseg == 1) ? final : static_cast<float*>(workspace);
+  rc = launch_template(tmpl, kp, dim3(1, nseg, bh), stream);
+  if (rc || nseg == 1) return rc;
+  ScanParams sp;
+  memset(&sp, 0, sizeof(sp));
+  sp.prob[0].ws = static_cast<float*>(workspace);
+  sp.prob[0].ext_final = final;
+  sp.nseg = nseg;
+  sp.rows = da;
+  sp.cols = dc;
+  sp.bh_count = bh;
+  sp.have_last = 1;
+  const int elems = da * dc;
+  fla_state_scan_kernel<<<dim3((elems + 255) / 256, bh, 1), 256, 0, stream>>>(sp);
+  ++g_last_launches;
+  return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
+
 int check_common(const FlaArgs* a, DeviceInfo** dev) {
   if (a == nullptr) return FLA_ERR_INVALID;
   if (a->batch <= 0 || a->heads <= 0 || a->seqlen <= 0 || a->dk <= 0 || a->dv <= 0)
@@ -346,7 +395,7 @@ int fla_sm100_auto_segments(const FlaArgs* a, int pass) {
   if (cudaGetDevice(&dev) == cudaSuccess)
     cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev);
   const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
-  return auto_segments(pass == 0 ? 1 : 3, a->batch * a->heads, nchunks, sm);
+  return auto_segments(pass == 1 ? 3 : 1, a->batch * a->heads, nchunks, sm);
 }
 
 size_t fla_sm100_workspace_bytes(const FlaArgs* a, int pass) {
@@ -357,7 +406,7 @@ size_t fla_sm100_workspace_bytes(const FlaArgs* a, int pass) {
   if (nseg <= 1) return 0;
   const int seg_chunks = (nchunks + nseg - 1) / nseg;
   nseg = (nchunks + seg_chunks - 1) / seg_chunks;
-  return segment_ws_bytes(pass == 0 ? 1 : 3, a->batch * a->heads, nseg, a->dk, a->dv) + 1024;
+  return segment_ws_bytes(pass == 1 ? 3 : 1, a->batch * a->heads, nseg, a->dk, a->dv) + 1024;
 }
 
 int fla_sm100_fwd(const FlaArgs* a) {
@@ -435,6 +484,23 @@ int fla_sm100_bwd(const FlaArgs* a) {
   if (rc) return rc;
   return run_products(&pv, 1, a->batch, a->heads, a->seqlen, a->dk, a->dv, nseg,
                       ws ? ws + 2 * third : nullptr, ws ? third : 0, a->status, stream, *dev);
+}
+
+int fla_sm100_state(const FlaArgs* a, int which) {
+  DeviceInfo* dev = nullptr;
+  g_last_launches = 0;
+  int rc = check_common(a, &dev);
+  if (rc) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  if (which == 0)
+    return run_state(operand(a->k, a->dk), operand(a->v, a->dv), a->batch, a->heads, a->seqlen,
+                     a->dk, a->dv, a->segments, a->s_final, a->workspace, a->workspace_bytes,
+                     a->status, stream, *dev);
+  if (which == 1)
+    return run_state(operand(a->q, a->dk), operand(a->d_o, a->dv), a->batch, a->heads, a->seqlen,
+                     a->dk, a->dv, a->segments, a->r_final, a->workspace, a->workspace_bytes,
+                     a->status, stream, *dev);
+  return FLA_ERR_INVALID;
 }
 
 }  // extern "C"

@@ -118,7 +118,7 @@ def _fptr(t: Optional[torch.Tensor], name: str, shape) -> Optional[int]:
     return t.data_ptr()
 
 
-def _call(pass_id: int, args: FlaArgs, device: torch.device) -> None:
+def _call(pass_id: int, args: FlaArgs, device: torch.device, which: int = 0) -> None:
     lib = _lib.load()
     with torch.cuda.device(device):
         args.stream = torch.cuda.current_stream(device).cuda_stream
@@ -129,8 +129,12 @@ def _call(pass_id: int, args: FlaArgs, device: torch.device) -> None:
             ws = torch.empty(need, dtype=torch.uint8, device=device)
             args.workspace = ws.data_ptr()
             args.workspace_bytes = need
-        fn = lib.fla_sm100_fwd if pass_id == 0 else lib.fla_sm100_bwd
-        rc = fn(ctypes.byref(args))
+        if pass_id == 0:
+            rc = lib.fla_sm100_fwd(ctypes.byref(args))
+        elif pass_id == 1:
+            rc = lib.fla_sm100_bwd(ctypes.byref(args))
+        else:
+            rc = lib.fla_sm100_state(ctypes.byref(args), which)
     if rc != 0:
         raise RuntimeError(f"flashlinear: libflashlinear_sm100 returned {rc}: {_lib.strerror(rc)}")
     if os.environ.get("FLA_DEBUG", "0") == "1":
@@ -198,6 +202,23 @@ def causal_dot_product_bwd(
         if view is not full:
             full.copy_(view)
     return dQ, dK, dV
+
+
+def chunk_state(b: torch.Tensor, c: torch.Tensor, segments: int = 0) -> torch.Tensor:
+    """fp32 [batch*heads, db, dc] sum over tokens of b_j^T c_j: with (k, v) the forward state S of
+    these tokens, with (q, dO) the backward state R. Used by sequence-sharded callers."""
+    _check_inputs(b, c)
+    B, H, N, db = b.shape
+    dc = c.shape[-1]
+    bv, cv = _kernel_view(b), _kernel_view(c)
+    out = torch.empty(B * H, db, dc, dtype=torch.float32, device=b.device)
+    a = FlaArgs()
+    a.batch, a.heads, a.seqlen, a.dk, a.dv = B, H, N, db, dc
+    a.k, a.v = _desc(bv), _desc(cv)
+    a.s_final = out.data_ptr()
+    a.segments = segments
+    _call(2, a, b.device, which=0)
+    return out
 
 
 # ------------------------------------------------------------------------------------------------

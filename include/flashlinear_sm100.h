@@ -84,7 +84,7 @@ typedef struct FlaArgs {
   void* stream;    /* cudaStream_t */
 } FlaArgs;
 
-/* pass: 0 = forward, 1 = backward */
+/* pass: 0 = forward, 1 = backward, 2 = fla_sm100_state */
 int fla_sm100_abi_version(void);
 const char* fla_sm100_strerror(int code);
 size_t fla_sm100_workspace_bytes(const FlaArgs* args, int pass);
@@ -97,6 +97,13 @@ int fla_sm100_fwd(const FlaArgs* args);
 /* replaces linear_flash_wrapper_bwd / linear_flash_wrapper_bwd_smallv_hd
  * (flashlinear/kernels/linear_attn_kernels.py:345, linear_attn_kernels_smallv_hd.py:363) */
 int fla_sm100_bwd(const FlaArgs* args);
+
+/* State of this call's tokens only, without an output: which = 0 writes
+ * s_final = sum_j k_j^T v_j (reads k, v), which = 1 writes r_final = sum_i q_i^T dO_i (reads q, d_o).
+ * Sequence-sharded callers exchange these [batch*heads, dk, dv] fp32 states between GPUs before
+ * calling fla_sm100_fwd / fla_sm100_bwd with s_init / r_init. The reference has no counterpart:
+ * its kernels are quadratic and keep no state (flashlinear/kernels/linear_attn_kernels.py:63). */
+int fla_sm100_state(const FlaArgs* args, int which);
 
 /* Number of kernels the last fwd / bwd call on this thread launched (for benchmarks). */
 int fla_sm100_last_launch_count(void);

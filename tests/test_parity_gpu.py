@@ -1,0 +1,288 @@
+"""GPU parity tests: the sm_100a kernels, called through the C ABI (via the ctypes wrappers), against
+the CPU oracle on the same inputs -- the committed fixtures that came from the reference's own
+naive path, seeded inputs at sizes the oracle finishes in seconds, and size-independent
+properties at the benchmark's full sizes.
+
+Tolerances (bf16 in / bf16 out, fp32 accumulation):
+    max relative error  max|a-b| / max|b|  <= 2e-2     (north-star bound for bf16)
+    Frobenius relative error               <  1e-2     (the reference tests' bound, test_attn.py:17)
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import linear_attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+MAX_REL_TOL = 2e-2
+FROB_TOL = 1e-2
+DEV = "cuda:0"
+
+
+def _ops():
+    from flashy_linear_attention_b200 import ops
+
+    return ops
+
+
+def _to_dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(torch.bfloat16).to(DEV)
+
+
+def _np(t):
+    return t.detach().float().cpu().numpy()
+
+
+def _check(name, got, want):
+    mr = orc.max_rel_error(got, want)
+    fr = orc.frobenius_rel_error(got, want)
+    assert mr <= MAX_REL_TOL and fr < FROB_TOL, f"{name}: max-rel {mr:.3e}, frobenius {fr:.3e}"
+
+
+def _run_and_check(q, k, v, dy, segments=0):
+    """q, k, v, dy: float32 numpy arrays holding bf16-representable values."""
+    ops = _ops()
+    tq, tk, tv, tdy = (_to_dev(t) for t in (q, k, v, dy))
+    out = ops.causal_dot_product_fwd(tq, tk, tv, segments=segments)
+    dq, dk, dv = ops.causal_dot_product_bwd(tdy, tq, tk, tv, segments=segments)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    q64, k64, v64, dy64 = (t.astype(np.float64) for t in (q, k, v, dy))
+    _check("out", _np(out), orc.linear_ref(q64, k64, v64))
+    rq, rk, rv = orc.linear_ref_grads(q64, k64, v64, dy64)
+    _check("dq", _np(dq), rq)
+    _check("dk", _np(dk), rk)
+    _check("dv", _np(dv), rv)
+
+
+def _golden_paths():
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    return [p for p in sorted(glob.glob(os.path.join(here, "*.npz"))) if "cfg1" not in p and "denominator" not in p]
+
+
+@pytest.mark.parametrize("path", _golden_paths(), ids=lambda p: os.path.basename(p)[:-4])
+def test_against_reference_fixture(path):
+    """Kernel results vs outputs of the reference's naive path stored in the fixture."""
+    ops = _ops()
+    g = np.load(path)
+    q, k, v, dy = (orc.bf16_round(g[n]) for n in ("q", "k", "v", "dy"))
+    exact_inputs = all(np.array_equal(orc.bf16_round(g[n]), g[n]) for n in ("q", "k", "v", "dy"))
+    tq, tk, tv, tdy = (_to_dev(t) for t in (q, k, v, dy))
+    out = ops.causal_dot_product_fwd(tq, tk, tv)
+    dq, dk, dv = ops.causal_dot_product_bwd(tdy, tq, tk, tv)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    # fixtures made from fp32 inputs were rounded to bf16 here, which alone costs ~4e-3
+    tol_scale = 1.0 if exact_inputs else 1.5
+    for name, got in (("out", out), ("dq", dq), ("dk", dk), ("dv", dv)):
+        mr = orc.max_rel_error(_np(got), g[name])
+        assert mr <= MAX_REL_TOL * tol_scale, (name, mr)
+
+
+def test_cfg1_with_pytorch_denominator():
+    """Benchmark configuration 1 (B2 H4 N256 D64, elu+1 inputs): kernel + the README's PyTorch
+    denominator, forward and backward through autograd, against the reference fixture."""
+    from flashlinear import LinearAttention
+
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    g = np.load(os.path.join(here, "ref_cfg1_b2h4_n256_d64_fp32_denominator.npz"))
+    B, H, N, dk, dv = (int(x) for x in g["shape"])
+    rng = np.random.Generator(np.random.PCG64(int(g["seed"])))
+    xq = rng.standard_normal((B, H, N, dk)).astype(np.float32)
+    xk = rng.standard_normal((B, H, N, dk)).astype(np.float32)
+    v = rng.standard_normal((B, H, N, dv)).astype(np.float32)
+    dy = rng.standard_normal((B, H, N, dv)).astype(np.float32)
+    q = torch.from_numpy(orc.elu_plus_one(xq)).to(DEV).requires_grad_(True)
+    k = torch.from_numpy(orc.elu_plus_one(xk)).to(DEV).requires_grad_(True)
+    vv = torch.from_numpy(v).to(DEV).requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        num = LinearAttention.apply(q, k, vv)
+    assert num.dtype == torch.bfloat16
+    den = (q * k.cumsum(-2)).sum(dim=-1, keepdim=True) + 1e-5  # README.md:29, fp32
+    res = num.float() / den
+    res.backward(torch.from_numpy(dy).to(DEV))
+    torch.cuda.synchronize()
+    rows = slice(None, None, int(g["row_stride"]))
+    for name, got in (("out", res), ("dq", q.grad), ("dk", k.grad), ("dv", vv.grad)):
+        mr = orc.max_rel_error(_np(got)[..., rows, :], g[name])
+        assert mr <= MAX_REL_TOL * 1.5, (name, mr)  # fp32 fixture inputs are rounded to bf16 here
+
+
+SHAPES = [
+    # B, H, N, dk, dv
+    (1, 1, 64, 64, 64),      # shorter than one chunk
+    (1, 1, 128, 128, 128),   # exactly one chunk
+    (2, 3, 256, 64, 64),
+    (1, 2, 320, 128, 128),   # chunk boundary inside: 128 + 128 + 64
+    (1, 2, 192, 32, 32),
+    (1, 1, 448, 83, 83),     # odd head dim: padded rows
+    (2, 2, 256, 96, 32),     # dk != dv
+    (1, 2, 384, 127, 16),
+    (1, 1, 1984, 128, 128),  # longest sequence of the reference's tests
+    (3, 31, 64, 16, 16),
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_seeded_inputs_against_oracle(shape):
+    B, H, N, dk, dv = shape
+    rng = np.random.default_rng(hash(shape) % (2 ** 31))
+    q = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, dk)).astype(np.float32)))
+    k = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, dk)).astype(np.float32)))
+    v = orc.bf16_round(rng.standard_normal((B, H, N, dv)).astype(np.float32))
+    dy = orc.bf16_round(rng.standard_normal((B, H, N, dv)).astype(np.float32))
+    _run_and_check(q, k, v, dy)
+
+
+@pytest.mark.parametrize("segments", [2, 3, 8])
+def test_segmented_equals_oracle(segments):
+    rng = np.random.default_rng(segments)
+    B, H, N, d = 1, 2, 1536, 64
+    q = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, d)).astype(np.float32)))
+    k = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, d)).astype(np.float32)))
+    v = orc.bf16_round(rng.standard_normal((B, H, N, d)).astype(np.float32))
+    dy = orc.bf16_round(rng.standard_normal((B, H, N, d)).astype(np.float32))
+    _run_and_check(q, k, v, dy, segments=segments)
+
+
+def test_kernel_rounding_matches_emulated_rounding_tightly():
+    """Against the oracle's emulation of the kernel's own rounding points the difference is only
+    summation order inside the MMAs: far below the bf16 tolerance."""
+    ops = _ops()
+    rng = np.random.default_rng(99)
+    B, H, N, d = 1, 2, 512, 64
+    q = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, d)).astype(np.float32)))
+    k = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, d)).astype(np.float32)))
+    v = orc.bf16_round(rng.standard_normal((B, H, N, d)).astype(np.float32))
+    out = ops.causal_dot_product_fwd(_to_dev(q), _to_dev(k), _to_dev(v))
+    emu, _ = orc.chunked_fwd(q, k, v, chunk=128, emulate_bf16=True)
+    # elements may differ by one bf16 ulp where the fp32 sums straddle a rounding boundary
+    assert orc.frobenius_rel_error(_np(out), emu) < 2e-3
+    assert orc.max_rel_error(_np(out), emu) < 8e-3
+
+
+def test_running_state_arguments():
+    """fwd(N) == fwd(first half) then fwd(second half, s_init); same for the backward with R."""
+    ops = _ops()
+    rng = np.random.default_rng(5)
+    B, H, N, d = 2, 2, 512, 128
+    h = 256
+    mk = lambda a: _to_dev(orc.bf16_round(a.astype(np.float32)))
+    q = mk(orc.elu_plus_one(rng.standard_normal((B, H, N, d))))
+    k = mk(orc.elu_plus_one(rng.standard_normal((B, H, N, d))))
+    v = mk(rng.standard_normal((B, H, N, d)))
+    dy = mk(rng.standard_normal((B, H, N, d)))
+    full = ops.causal_dot_product_fwd(q, k, v)
+    fq, fk, fv = ops.causal_dot_product_bwd(dy, q, k, v)
+    s_mid = torch.empty(B * H, d, d, dtype=torch.float32, device=DEV)
+    q1, k1, v1, dy1 = (t[:, :, :h].contiguous() for t in (q, k, v, dy))
+    q2, k2, v2, dy2 = (t[:, :, h:].contiguous() for t in (q, k, v, dy))
+    o1 = ops.causal_dot_product_fwd(q1, k1, v1, s_final=s_mid)
+    o2 = ops.causal_dot_product_fwd(q2, k2, v2, s_init=s_mid)
+    # state read-out equals the state-only entry point and the oracle
+    s_only = ops.chunk_state(k1, v1)
+    want_s = np.matmul(np.swapaxes(_np(k1).astype(np.float64), -1, -2), _np(v1).astype(np.float64)).reshape(B * H, d, d)
+    assert orc.max_rel_error(_np(s_mid), want_s) < 1e-4
+    assert orc.max_rel_error(_np(s_only), want_s) < 1e-4
+    r_mid = torch.empty(B * H, d, d, dtype=torch.float32, device=DEV)
+    dq2, dk2, dv2 = ops.causal_dot_product_bwd(dy2, q2, k2, v2, s_init=s_mid, r_final=r_mid)
+    dq1, dk1, dv1 = ops.causal_dot_product_bwd(dy1, q1, k1, v1, r_init=r_mid)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    # the split run equals the unsplit one (the state is carried in fp32)
+    for a, b, full_t in ((o1, o2, full), (dq1, dq2, fq), (dk1, dk2, fk), (dv1, dv2, fv)):
+        got = torch.cat([a, b], dim=2)
+        assert orc.frobenius_rel_error(_np(got), _np(full_t)) < 2e-3
+
+
+def test_strided_and_offset_inputs():
+    """Per-tensor strides: q from a fused [B,N,3,H,D] projection, transposed v, expanded grad."""
+    ops = _ops()
+    torch.manual_seed(0)
+    B, H, N, d = 2, 3, 256, 64
+    qkv = torch.randn(B, N, 3, H, d, device=DEV).to(torch.bfloat16)
+    q = torch.nn.functional.softplus(qkv[:, :, 0]).transpose(1, 2)
+    k = torch.nn.functional.softplus(qkv[:, :, 1]).transpose(1, 2)
+    v = qkv[:, :, 2].transpose(1, 2)          # non-contiguous view, stride_n = 3*H*d
+    assert not v.is_contiguous()
+    out = ops.causal_dot_product_fwd(q, k, v)
+    ref = ops.causal_dot_product_fwd(q.contiguous(), k.contiguous(), v.contiguous())
+    assert torch.equal(out, ref)
+    dy = torch.randn(1, 1, N, d, device=DEV).to(torch.bfloat16).expand(B, H, N, d)  # zero strides
+    g1 = ops.causal_dot_product_bwd(dy, q, k, v)
+    g2 = ops.causal_dot_product_bwd(dy.contiguous(), q.contiguous(), k.contiguous(), v.contiguous())
+    for a, b in zip(g1, g2):
+        assert torch.equal(a, b)
+    qn = _np(q).astype(np.float64); kn = _np(k).astype(np.float64); vn = _np(v).astype(np.float64)
+    _check("out", _np(out), orc.linear_ref(qn, kn, vn))
+
+
+def test_autocast_and_dtype_behaviour():
+    """custom_fwd(cast_inputs=bf16): fp32 inputs are cast under autocast (linear_attn.py:13);
+    outside autocast a non-bf16 input is an error rather than a silent wrong result."""
+    from flashlinear import LinearAttention
+
+    q = torch.rand(1, 2, 128, 64, device=DEV, requires_grad=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = LinearAttention.apply(q, q, q)
+    assert out.dtype == torch.bfloat16
+    out.float().sum().backward()
+    assert q.grad is not None and q.grad.dtype == torch.float32
+    with pytest.raises(TypeError):
+        LinearAttention.apply(q, q, q)
+
+
+def test_outputs_are_fully_written():
+    """NaN-poisoned allocator blocks must be completely overwritten by the kernels."""
+    ops = _ops()
+    B, H, N, d = 1, 3, 320, 64
+    poison = torch.full((B, H, N, d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    del poison  # returns the block to the caching allocator; empty_like below reuses it
+    q = torch.rand(B, H, N, d, device=DEV).to(torch.bfloat16)
+    out = ops.causal_dot_product_fwd(q, q, q)
+    dq, dk, dv = ops.causal_dot_product_bwd(q, q, q, q)
+    for t in (out, dq, dk, dv):
+        assert not torch.isnan(t.float()).any()
+
+
+@pytest.mark.parametrize("cfg", [(8, 16, 4096, 64), (4, 32, 8192, 128)], ids=["cfg2", "cfg3"])
+def test_full_size_properties(cfg):
+    """Benchmark sizes, checked through properties that need no O(N^2) oracle:
+    (1) with q = all-ones the product collapses to a cumulative sum, out_i = cumsum_j (sum_d k_jd) v_j;
+    (2) linearity in v; (3) segmented == unsegmented; (4) one head against the naive oracle path."""
+    ops = _ops()
+    B, H, N, d = cfg
+    gen = torch.Generator(device=DEV).manual_seed(1)
+    k = (torch.nn.functional.elu(torch.randn(B, H, N, d, device=DEV, generator=gen)) + 1).to(torch.bfloat16)
+    q = (torch.nn.functional.elu(torch.randn(B, H, N, d, device=DEV, generator=gen)) + 1).to(torch.bfloat16)
+    v = torch.randn(B, H, N, d, device=DEV, generator=gen).to(torch.bfloat16)
+    ones = torch.ones_like(q)
+    out1 = ops.causal_dot_product_fwd(ones, k, v)
+    want1 = torch.cumsum(k.float().sum(-1, keepdim=True).double() * v.double(), dim=2)
+    rel = ((out1.double() - want1).abs().max() / want1.abs().max()).item()
+    assert rel <= MAX_REL_TOL, rel
+    out = ops.causal_dot_product_fwd(q, k, v)
+    out_neg = ops.causal_dot_product_fwd(q, k, -v)
+    assert torch.equal(out, -out_neg)
+    v2 = torch.randn(B, H, N, d, device=DEV, generator=gen).to(torch.bfloat16)
+    lhs = ops.causal_dot_product_fwd(q, k, (v.float() + v2.float()).to(torch.bfloat16)).float()
+    rhs = out.float() + ops.causal_dot_product_fwd(q, k, v2).float()
+    assert (torch.linalg.norm(lhs - rhs) / torch.linalg.norm(rhs)).item() < FROB_TOL
+    seg = ops.causal_dot_product_fwd(q, k, v, segments=4)
+    assert (torch.linalg.norm(seg.float() - out.float()) / torch.linalg.norm(out.float())).item() < 2e-3
+    dy = torch.randn(B, H, N, d, device=DEV, generator=gen).to(torch.bfloat16)
+    dq, dk, dv = ops.causal_dot_product_bwd(dy, q, k, v)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    # one head, full length, against the oracle (naive O(N^2) path on the CPU)
+    b, h = B - 1, H - 1
+    qs, ks, vs, dys = (_np(t[b, h]).astype(np.float64) for t in (q, k, v, dy))
+    _check("out[head]", _np(out[b, h]), orc.linear_ref(qs, ks, vs))
+    rq, rk, rv = orc.linear_ref_grads(qs, ks, vs, dys)
+    _check("dq[head]", _np(dq[b, h]), rq)
+    _check("dk[head]", _np(dk[b, h]), rk)
+    _check("dv[head]", _np(dv[b, h]), rv)
