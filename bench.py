@@ -16,14 +16,12 @@ the host cores, on a bounded sample of the same workload.
 from __future__ import annotations
 
 import argparse
-import ctypes
 import json
 import os
 import statistics
 import subprocess
 import sys
 import threading
-import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -34,6 +32,7 @@ WORKLOADS = {
     # name: (B, H, N, dk, dv)
     "cfg2": (8, 16, 4096, 64, 64),
     "cfg3": (4, 32, 8192, 128, 128),
+    "cfg3_small": (4, 32, 1024, 128, 128),  # cfg3's head count at N=1024: sized for ncu captures
     "cfg5": (1, 32, 65536, 128, 128),
 }
 METRIC = "fwd+bwd Mtokens/s, N=8K D=128 bf16, 1/2/4/8 B200; % tensor/HBM roofline"
