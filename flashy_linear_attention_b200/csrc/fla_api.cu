@@ -46,6 +46,9 @@ EncodeTiledFn get_encode_fn() {
 }
 
 thread_local int g_last_launches = 0;
+#ifdef FLA_TRACE
+long long* g_trace = nullptr;  // tracing build only: timeline buffer handed to every launch
+#endif
 
 struct Operand {
   const void* ptr;
@@ -201,7 +204,11 @@ size_t segment_ws_bytes(int nprob, int bh, int nseg, int rows, int cols) {
 }
 
 template <int D>
-int launch_kernel(const KernelParams& kp, dim3 grid, cudaStream_t stream) {
+int launch_kernel(const KernelParams& kp_in, dim3 grid, cudaStream_t stream) {
+  KernelParams kp = kp_in;
+#ifdef FLA_TRACE
+  kp.trace = g_trace;
+#endif
   fla::fla_chunk_kernel<D, D><<<grid, fla::kThreads, fla::Cfg<D, D>::SMEM_BYTES, stream>>>(kp);
   ++g_last_launches;
   return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
@@ -371,6 +378,10 @@ int check_common(const FlaArgs* a, DeviceInfo** dev) {
 extern "C" {
 
 int fla_sm100_abi_version(void) { return FLA_ABI_VERSION; }
+
+#ifdef FLA_TRACE
+void fla_sm100_set_trace(long long* buf) { g_trace = buf; }
+#endif
 
 const char* fla_sm100_strerror(int code) {
   switch (code) {

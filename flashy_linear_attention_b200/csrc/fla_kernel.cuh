@@ -8,19 +8,25 @@
 // product with the operands permuted (see fla_api.cu), which replaces the quadratic tile loops of
 // flashlinear/kernels/linear_attn_kernels.py:63-85 (fwd), :171-200 and :283-302 (bwd).
 //
-// CTA layout (320 threads, one CTA per SM):
-//   warp 0      TMA producer: Q, K, V chunk tiles -> shared memory (128-byte swizzle), mbarrier ring
-//   warp 1      tcgen05.mma issuer (one thread) and TMEM owner
-//   warps 2-5   converter group: P fp32 (TMEM) -> mask -> bf16 (TMEM, A operand);
-//               S fp32 (TMEM) -> bf16 (shared memory, B operand)
-//   warps 6-9   epilogue group: O fp32 (TMEM) -> bf16 -> shared memory -> TMA store
+// CTA layout (448 threads, one CTA per SM):
+//   warp 0        TMA producer: Q, K, V chunk tiles -> a ring of shared-memory slots (128B swizzle)
+//   warp 1        tcgen05.mma issuer (one thread) and TMEM owner
+//   warps 2-5     converter group A  } P fp32 (TMEM) -> mask -> bf16 (TMEM, A operand of P V)
+//   warps 6-9     converter group B  } S fp32 (TMEM) -> bf16 (shared memory, B operand of Q S);
+//                                      each group owns one half of the columns
+//   warps 10-13   epilogue group: O fp32 (TMEM) -> bf16 -> staging buffer -> TMA store
+//
+// MMA issue order per chunk i (steady state):  O = Q_i Sb_{i-1};  S += K_i^T V_i;  O += Pb_i V_i;
+// P = Q_{i+1} K_{i+1}^T.  The score tile of the NEXT chunk is issued last so that its conversion
+// overlaps the first two MMAs of that chunk, and the state conversion overlaps the last two of
+// this one; the only loop-carried dependency is the state.
 #pragma once
 #include "ptx.cuh"
 
 namespace fla {
 
-constexpr int kChunk = 128;    // tokens per chunk (= MMA M)
-constexpr int kThreads = 320;  // 10 warps
+constexpr int kChunk = 128;                // tokens per chunk (= MMA M)
+constexpr int kThreads = 448;              // 14 warps
 constexpr int kGroupBytes = kChunk * 128;  // one 64-column group of a chunk tile: 128 rows x 128 B
 
 struct Problem {
@@ -41,31 +47,47 @@ struct KernelParams {
   int st_cols;
   int skip_last_segment;  // mode 1: the last segment's sum is not needed
   int* status;     // device word, bit 0 set when a bounded wait ran out; may be null
+  long long* trace;  // timeline buffer of the tracing build (FLA_TRACE), else unused
 };
+
+#ifdef FLA_TRACE
+// Tracing build only: lane 0 of the warps of the first CTA records clock64() at pipeline events,
+// laid out [event][chunk < 64].
+#define FLA_TRACE_DECL                                                                        \
+  const bool trace_on = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 &&          \
+                        blockIdx.z == 0 && (threadIdx.x & 31) == 0;
+#define FLA_TRACE_EVENT(e, i)                                        \
+  do {                                                               \
+    if (trace_on && (i) < 64) p.trace[(e) * 64 + (i)] = clock64();   \
+  } while (0)
+#else
+#define FLA_TRACE_DECL
+#define FLA_TRACE_EVENT(e, i) do { } while (0)
+#endif
 
 template <int DK, int DV>
 struct Cfg {
-  static_assert(DK % 64 == 0 && DV % 64 == 0 && DK <= 128 && DV <= 128, "unsupported head dims");
+  static_assert(DK == DV, "tile ring assumes equally sized q/k and v tiles");
+  static_assert(DK % 64 == 0 && DK <= 128, "unsupported head dims");
   static constexpr int GK = DK / 64;
   static constexpr int GV = DV / 64;
-  static constexpr int Q_BYTES = GK * kGroupBytes;
-  static constexpr int K_BYTES = GK * kGroupBytes;
-  static constexpr int V_BYTES = GV * kGroupBytes;
-  static constexpr int STAGE_BYTES = Q_BYTES + K_BYTES + V_BYTES;
-  static constexpr int SB_BYTES = GV * DK * 128;  // bf16 state as MMA B operand
-  static constexpr int BAR_BYTES = 256;
+  static constexpr int TILE_BYTES = GK * kGroupBytes;  // one chunk tile of q, k or v
+  static constexpr int SB_BYTES = GV * DK * 128;       // bf16 state as MMA B operand
+  static constexpr int OST_BYTES = GV * kGroupBytes;   // output staging for the TMA store
+  static constexpr int BAR_BYTES = 512;
   static constexpr int SMEM_LIMIT = 232448;  // 227 KB
-  static constexpr int NSTAGES_RAW = (SMEM_LIMIT - 1024 - BAR_BYTES - SB_BYTES) / STAGE_BYTES;
-  static constexpr int NSTAGES = NSTAGES_RAW > 4 ? 4 : NSTAGES_RAW;
-  static_assert(NSTAGES >= 2, "need at least two stages");
-  static constexpr int SMEM_BYTES = 1024 + NSTAGES * STAGE_BYTES + SB_BYTES + BAR_BYTES;
-  // The epilogue stages O in the Q buffer of the chunk it belongs to.
-  static_assert(V_BYTES <= Q_BYTES, "O staging needs dv <= dk tiles");
+  static constexpr int NSLOT_RAW =
+      (SMEM_LIMIT - 1024 - BAR_BYTES - SB_BYTES - OST_BYTES) / TILE_BYTES;
+  static constexpr int NSLOT = NSLOT_RAW > 9 ? 9 : NSLOT_RAW;
+  static_assert(NSLOT >= 5, "need at least five tile slots");
+  static constexpr int SMEM_BYTES = 1024 + NSLOT * TILE_BYTES + SB_BYTES + OST_BYTES + BAR_BYTES;
+  static_assert(SMEM_BYTES <= SMEM_LIMIT, "shared memory budget");
+  static_assert((2 * NSLOT + 8) * 8 + 16 <= BAR_BYTES, "barrier area");
   // TMEM columns (32-bit each, 128 lanes)
-  static constexpr int P_COL = 0;            // P fp32: 128 columns
-  static constexpr int PB_COL = 128;         // P bf16 (two per column): 64 columns
-  static constexpr int O_COL = 192;          // O fp32: DV columns
-  static constexpr int S_COL = 192 + DV;     // S fp32: DV columns, lane = dk index
+  static constexpr int P_COL = 0;         // P fp32: 128 columns
+  static constexpr int PB_COL = 128;      // P bf16 (two per column): 64 columns
+  static constexpr int O_COL = 192;       // O fp32: DV columns
+  static constexpr int S_COL = 192 + DV;  // S fp32: DV columns, lane = dk index
   static constexpr int TMEM_COLS = 512;
   static_assert(S_COL + DV <= TMEM_COLS, "TMEM budget");
 };
@@ -74,41 +96,46 @@ template <int DK, int DV>
 __global__ void __launch_bounds__(kThreads, 1)
 fla_chunk_kernel(const __grid_constant__ KernelParams p) {
   using cfg = Cfg<DK, DV>;
-  constexpr int NS = cfg::NSTAGES;
+  constexpr int NSLOT = cfg::NSLOT;
   extern __shared__ uint8_t smem_raw[];
 
-  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
-  const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
-  uint8_t* smem_gen = smem_raw + (smem_base - raw_addr);
-
-  const uint32_t sb_addr = smem_base + NS * cfg::STAGE_BYTES;
-  const uint32_t bar_base = sb_addr + cfg::SB_BYTES;
-  auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (NS + s); };
-  const uint32_t p_full = bar_base + 8u * (2 * NS + 0);
-  const uint32_t pb_ready = bar_base + 8u * (2 * NS + 1);
-  const uint32_t o_full = bar_base + 8u * (2 * NS + 2);
-  const uint32_t o_free = bar_base + 8u * (2 * NS + 3);
-  const uint32_t s_full = bar_base + 8u * (2 * NS + 4);
-  const uint32_t sb_ready = bar_base + 8u * (2 * NS + 5);
-  const uint32_t o_staged = bar_base + 8u * (2 * NS + 6);
-  const uint32_t holder_off = NS * cfg::STAGE_BYTES + cfg::SB_BYTES + 8u * (2 * NS + 7);
-  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_gen + holder_off);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + holder_off + 4);
-
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);  // provably warp-uniform
   const int lane = threadIdx.x & 31;
   const int prob_idx = blockIdx.x;
   const int g = blockIdx.y;
   const int nseg = gridDim.y;
   const int bh = blockIdx.z;
+  const int mode = p.mode;
+  FLA_TRACE_DECL
+  if (mode == 1 && p.skip_last_segment && g == nseg - 1) return;  // whole CTA, before any setup
+
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - raw_addr);
+
+  const uint32_t sb_addr = smem_base + NSLOT * cfg::TILE_BYTES;
+  const uint32_t ost_addr = sb_addr + cfg::SB_BYTES;
+  const uint32_t bar_base = ost_addr + cfg::OST_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (NSLOT + s); };
+  const uint32_t p_full = bar_base + 8u * (2 * NSLOT + 0);
+  const uint32_t pb_ready = bar_base + 8u * (2 * NSLOT + 1);
+  const uint32_t o_full = bar_base + 8u * (2 * NSLOT + 2);
+  const uint32_t qs_ready = bar_base + 8u * (2 * NSLOT + 3);
+  const uint32_t s_full = bar_base + 8u * (2 * NSLOT + 4);
+  const uint32_t o_staged = bar_base + 8u * (2 * NSLOT + 6);
+  const uint32_t ost_free = bar_base + 8u * (2 * NSLOT + 7);
+  const uint32_t holder_off =
+      NSLOT * cfg::TILE_BYTES + cfg::SB_BYTES + cfg::OST_BYTES + 8u * (2 * NSLOT + 8);
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_gen + holder_off);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + holder_off + 4);
+
   const Problem& pr = p.prob[prob_idx];
   const int h = bh % p.heads;
   const int b = bh / p.heads;
   const int chunk0 = g * p.seg_chunks;
   const int n_iter = min(p.seg_chunks, p.nchunks - chunk0);
   const bool reverse = pr.reverse != 0;
-  const int mode = p.mode;
   const bool has_init = (mode == 0) && (pr.s_init != nullptr);
   const size_t st_elems = static_cast<size_t>(p.st_rows) * p.st_cols;
   const size_t st_index = (static_cast<size_t>(bh) * nseg + g) * st_elems;
@@ -117,22 +144,24 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
     return st_index + (st_trans ? static_cast<size_t>(col) * p.st_rows + row
                                 : static_cast<size_t>(row) * p.st_cols + col);
   };
-  if (mode == 1 && p.skip_last_segment && g == nseg - 1) return;  // whole CTA, before any setup
+  // Tiles are numbered in load order: chunk i holds tiles tpc*i + {0: q, 1: k, 2: v} (mode 0) or
+  // 2*i + {0: k, 1: v} (mode 1); tile t lives in slot t % NSLOT during ring pass t / NSLOT.
+  const int tpc = (mode == 0) ? 3 : 2;
 
   // ------------------------------------------------------------------ setup
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    for (int s = 0; s < NS; ++s) {
+    for (int s = 0; s < NSLOT; ++s) {
       ptx::mbar_init(full_bar(s), 1);
-      ptx::mbar_init(empty_bar(s), mode == 0 ? 2 : 1);
+      ptx::mbar_init(empty_bar(s), 1);
     }
     ptx::mbar_init(p_full, 1);
-    ptx::mbar_init(pb_ready, 128);
+    ptx::mbar_init(pb_ready, 256);
     ptx::mbar_init(o_full, 1);
-    ptx::mbar_init(o_free, 128);
+    ptx::mbar_init(qs_ready, 256 + 128);  // state converted (256) and O drained (128)
     ptx::mbar_init(s_full, 1);
-    ptx::mbar_init(sb_ready, 128);
     ptx::mbar_init(o_staged, 128);
+    ptx::mbar_init(ost_free, 1);
     ptx::fence_barrier_init();
     ptx::fence_proxy_async_smem();
   }
@@ -153,42 +182,51 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
+  // Wait executed by a whole warp; the outcome is made uniform so that the warp never diverges
+  // around .sync.aligned instructions.
+  auto wait_uniform = [&](uint32_t bar, uint32_t parity) {
+    const int ok = ptx::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+    return __all_sync(0xffffffffu, ok) != 0;
+  };
   auto mem_chunk = [&](int i) { return reverse ? (p.nchunks - 1 - (chunk0 + i)) : (chunk0 + i); };
-  auto stage_addr = [&](int s) { return smem_base + static_cast<uint32_t>(s) * cfg::STAGE_BYTES; };
+  auto slot_addr = [&](int t) {
+    return smem_base + static_cast<uint32_t>(t % NSLOT) * cfg::TILE_BYTES;
+  };
 
   if (warp == 0) {
     // ================================================================ TMA producer
-    for (int i = 0; i < n_iter; ++i) {
-      int ok = 1;
-      if (lane == 0) {
-        const int s = i % NS;
-        const uint32_t ph = (i / NS) & 1;
-        ok = ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag) ? 1 : 0;
-        if (ok) {
-          const uint32_t st = stage_addr(s);
-          const int tok = mem_chunk(i) * kChunk;
-          const uint32_t bytes = (mode == 0 ? cfg::Q_BYTES : 0) + cfg::K_BYTES + cfg::V_BYTES;
-          ptx::mbar_expect_tx(full_bar(s), bytes);
-          if (mode == 0) {
+    // The whole warp runs the loop (so that addresses and coordinates stay warp-uniform); one
+    // elected lane issues. In mode 0 the q and k tiles of a chunk complete on the q tile's barrier.
+    const bool leader = ptx::elect_one();
+    const int n_tiles = n_iter * tpc;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int s = t % NSLOT;
+      const uint32_t ph = (t / NSLOT) & 1;
+      if (!wait_uniform(empty_bar(s), ph ^ 1u)) break;
+      const int i = t / tpc;
+      const int which = t - i * tpc + (mode == 0 ? 0 : 1);  // 0 q, 1 k, 2 v
+      const CUtensorMap* map = (which == 0) ? &pr.q : (which == 1 ? &pr.k : &pr.v);
+      const uint32_t dst = slot_addr(t);
+      const int tok = mem_chunk(i) * kChunk;
+      // barrier that the tile's bytes complete on, and the bytes armed on it at this point
+      const uint32_t bar = (mode == 0 && which == 1) ? full_bar((t - 1) % NSLOT) : full_bar(s);
+      if (leader) {
+        if (mode == 0 && which == 0) ptx::mbar_expect_tx(bar, 2 * cfg::TILE_BYTES);
+        if (mode != 0 || which == 2) ptx::mbar_expect_tx(bar, cfg::TILE_BYTES);
+        // The k slot's own barrier is not waited on; complete its phase so that the parity of
+        // later ring passes stays in step.
+        if (mode == 0 && which == 1) ptx::mbar_arrive(full_bar(s));
 #pragma unroll
-            for (int gg = 0; gg < cfg::GK; ++gg)
-              ptx::tma_load_4d(st + gg * kGroupBytes, &pr.q, full_bar(s), gg * 64, tok, h, b);
-          }
-#pragma unroll
-          for (int gg = 0; gg < cfg::GK; ++gg)
-            ptx::tma_load_4d(st + cfg::Q_BYTES + gg * kGroupBytes, &pr.k, full_bar(s), gg * 64, tok,
-                             h, b);
-#pragma unroll
-          for (int gg = 0; gg < cfg::GV; ++gg)
-            ptx::tma_load_4d(st + cfg::Q_BYTES + cfg::K_BYTES + gg * kGroupBytes, &pr.v,
-                             full_bar(s), gg * 64, tok, h, b);
-        }
+        for (int gg = 0; gg < cfg::GK; ++gg)
+          ptx::tma_load_4d(dst + gg * kGroupBytes, map, bar, gg * 64, tok, h, b);
+        FLA_TRACE_EVENT(28 + which, i);
       }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
+      __syncwarp();
     }
   } else if (warp == 1) {
     // ================================================================ MMA issuer
+    // The whole warp runs the loop with warp-uniform operands; one elected lane issues the
+    // tcgen05.mma / tcgen05.commit instructions.
     constexpr uint32_t IDESC_QK = ptx::make_idesc(128, kChunk, false, false);  // P  = Q K^T
     constexpr uint32_t IDESC_PV = ptx::make_idesc(128, DV, false, true);       // O += Pb V
     constexpr uint32_t IDESC_QS = ptx::make_idesc(128, DV, false, true);       // O  = Q Sb
@@ -197,83 +235,126 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
     const uint32_t tPb = tmem_base + cfg::PB_COL;
     const uint32_t tO = tmem_base + cfg::O_COL;
     const uint32_t tS = tmem_base + cfg::S_COL;
-    uint32_t sb_waits = 0;
-    for (int i = 0; i < n_iter; ++i) {
-      int ok = 1;
-      if (lane == 0) {
-        const int s = i % NS;
-        const uint32_t ph = (i / NS) & 1;
-        const uint32_t q_addr = stage_addr(s);
-        const uint32_t k_addr = q_addr + cfg::Q_BYTES;
-        const uint32_t v_addr = k_addr + cfg::K_BYTES;
+    const bool leader = ptx::elect_one();
+    auto wait_tile = [&](int t) { return wait_uniform(full_bar(t % NSLOT), (t / NSLOT) & 1); };
+    auto release_tile = [&](int t) {
+      if (leader) ptx::tc_commit(empty_bar(t % NSLOT));
+    };
+    // P = Q K^T of chunk i (both operands K-major, 16 columns of dk per instruction)
+    auto issue_qk = [&](int i) {
+      if (!wait_tile(3 * i)) return false;  // covers the k tile too
+      ptx::tc_fence_after();
+      const uint32_t q_lo = ptx::desc_lo(slot_addr(3 * i), 16);
+      const uint32_t k_lo = ptx::desc_lo(slot_addr(3 * i + 1), 16);
+      if (leader) {
+#pragma unroll
+        for (int kk = 0; kk < DK / 16; ++kk) {
+          const uint32_t off = ((kk >> 2) * kGroupBytes + (kk & 3) * 32) >> 4;
+          ptx::mma_ss(tP, q_lo + off, k_lo + off, ptx::kDescHi, IDESC_QK, kk > 0 ? 1u : 0u);
+        }
+        ptx::tc_commit(p_full);
+      }
+      __syncwarp();
+      return true;
+    };
+    if (mode == 0) {
+      uint32_t qs_waits = 0;
+      bool ok = issue_qk(0);
+      for (int i = 0; ok && i < n_iter; ++i) {
+        // descriptor low words: q K-major; k, v and the state buffer MN-major (64-column groups
+        // kGroupBytes resp. DK*128 bytes apart)
+        const uint32_t q_lo = ptx::desc_lo(slot_addr(3 * i), 16);
+        const uint32_t k_lo = ptx::desc_lo(slot_addr(3 * i + 1), kGroupBytes);
+        const uint32_t v_lo = ptx::desc_lo(slot_addr(3 * i + 2), kGroupBytes);
+        const uint32_t sb_lo = ptx::desc_lo(sb_addr, DK * 128);
         const bool have_state = (i > 0) || has_init;
-        do {
-          if (!ptx::mbar_wait(full_bar(s), ph, abort_flag)) { ok = 0; break; }
+        const uint32_t acc0 = have_state ? 1u : 0u;
+        FLA_TRACE_EVENT(0, i);
+        // ---- O = Q Sb  (inter-chunk part; Sb is dk x dv, dv contiguous: MN-major B). Needs the
+        // converted state of the previous chunk and the O accumulator drained by the epilogue.
+        if (have_state) {
+          if (!wait_uniform(qs_ready, qs_waits & 1)) break;
+          ++qs_waits;
+          FLA_TRACE_EVENT(2, i);
           ptx::tc_fence_after();
-          if (mode == 0) {
-            // ---- P = Q K^T  (both operands K-major, 16 columns of dk per instruction)
+          if (leader) {
 #pragma unroll
             for (int kk = 0; kk < DK / 16; ++kk) {
-              const uint32_t off = (kk >> 2) * kGroupBytes + (kk & 3) * 32;
-              ptx::mma_ss(tP, ptx::make_smem_desc(q_addr + off, 16, 1024),
-                          ptx::make_smem_desc(k_addr + off, 16, 1024), IDESC_QK, kk > 0);
+              const uint32_t off = ((kk >> 2) * kGroupBytes + (kk & 3) * 32) >> 4;
+              ptx::mma_ss(tO, q_lo + off, sb_lo + kk * (2048 >> 4), ptx::kDescHi, IDESC_QS,
+                          kk > 0 ? 1u : 0u);
             }
-            ptx::tc_commit(p_full);
-            // ---- O = Q Sb  (inter-chunk part; Sb is dk x dv, dv contiguous: MN-major B)
-            if (i > 0) {
-              if (!ptx::mbar_wait(o_free, (i - 1) & 1, abort_flag)) { ok = 0; break; }
-            }
-            if (have_state) {
-              if (!ptx::mbar_wait(sb_ready, sb_waits & 1, abort_flag)) { ok = 0; break; }
-              ++sb_waits;
-              ptx::tc_fence_after();
-#pragma unroll
-              for (int kk = 0; kk < DK / 16; ++kk) {
-                const uint32_t off = (kk >> 2) * kGroupBytes + (kk & 3) * 32;
-                ptx::mma_ss(tO, ptx::make_smem_desc(q_addr + off, 16, 1024),
-                            ptx::make_smem_desc(sb_addr + kk * 2048, DK * 128, 1024), IDESC_QS,
-                            kk > 0);
-              }
-            }
-            // ---- O += Pb V  (A from TMEM: 16 bf16 = 8 columns per instruction; V MN-major)
-            if (!ptx::mbar_wait(pb_ready, i & 1, abort_flag)) { ok = 0; break; }
-            ptx::tc_fence_after();
-#pragma unroll
-            for (int kk = 0; kk < kChunk / 16; ++kk) {
-              ptx::mma_ts(tO, tPb + kk * 8,
-                          ptx::make_smem_desc(v_addr + kk * 2048, kGroupBytes, 1024), IDESC_PV,
-                          (have_state || kk > 0) ? 1u : 0u);
-            }
-            ptx::tc_commit(o_full);
           }
-          // ---- S += K^T V  (both operands MN-major: the token index is the MMA K dimension).
-          // For DK = 64 the instruction still spans 128 rows; the upper 64 read whatever follows
-          // the K tile in shared memory and land in TMEM lanes nobody reads.
+        }
+        release_tile(3 * i);  // q: read by the score MMA (issued earlier) and the one above
+        FLA_TRACE_EVENT(3, i);
+        // ---- S += K^T V  (both operands MN-major: the token index is the MMA K dimension).
+        // For DK = 64 the instruction still spans 128 rows; the upper 64 read whatever follows
+        // the K tile in shared memory and land in TMEM lanes nobody reads.
+        if (!wait_tile(3 * i + 2)) break;
+        FLA_TRACE_EVENT(4, i);
+        ptx::tc_fence_after();
+        if (leader) {
 #pragma unroll
           for (int kk = 0; kk < kChunk / 16; ++kk) {
-            ptx::mma_ss(tS, ptx::make_smem_desc(k_addr + kk * 2048, kGroupBytes, 1024),
-                        ptx::make_smem_desc(v_addr + kk * 2048, kGroupBytes, 1024), IDESC_KV,
-                        (have_state || kk > 0) ? 1u : 0u);
+            ptx::mma_ss(tS, k_lo + kk * (2048 >> 4), v_lo + kk * (2048 >> 4), ptx::kDescHi,
+                        IDESC_KV, kk > 0 ? 1u : acc0);
           }
-          if (mode == 0 || i == n_iter - 1) ptx::tc_commit(s_full);
-          ptx::tc_commit(empty_bar(s));
-        } while (false);
+          ptx::tc_commit(s_full);
+        }
+        release_tile(3 * i + 1);
+        FLA_TRACE_EVENT(5, i);
+        // ---- O += Pb V  (A from TMEM: 16 bf16 = 8 columns per instruction; V MN-major)
+        if (!wait_uniform(pb_ready, i & 1)) break;
+        FLA_TRACE_EVENT(6, i);
+        ptx::tc_fence_after();
+        if (leader) {
+#pragma unroll
+          for (int kk = 0; kk < kChunk / 16; ++kk) {
+            ptx::mma_ts(tO, tPb + kk * 8, v_lo + kk * (2048 >> 4), ptx::kDescHi, IDESC_PV,
+                        kk > 0 ? 1u : acc0);
+          }
+          ptx::tc_commit(o_full);
+        }
+        release_tile(3 * i + 2);
+        FLA_TRACE_EVENT(7, i);
+        // ---- score tile of the next chunk (P fp32 is free: its conversion was awaited above)
+        if (i + 1 < n_iter) ok = issue_qk(i + 1);
+        FLA_TRACE_EVENT(8, i);
       }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
+    } else {
+      for (int i = 0; i < n_iter; ++i) {
+        if (!wait_tile(2 * i) || !wait_tile(2 * i + 1)) break;
+        ptx::tc_fence_after();
+        const uint32_t k_lo = ptx::desc_lo(slot_addr(2 * i), kGroupBytes);
+        const uint32_t v_lo = ptx::desc_lo(slot_addr(2 * i + 1), kGroupBytes);
+        if (leader) {
+#pragma unroll
+          for (int kk = 0; kk < kChunk / 16; ++kk) {
+            ptx::mma_ss(tS, k_lo + kk * (2048 >> 4), v_lo + kk * (2048 >> 4), ptx::kDescHi,
+                        IDESC_KV, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+        }
+        release_tile(2 * i);
+        release_tile(2 * i + 1);
+        if (leader && i == n_iter - 1) ptx::tc_commit(s_full);
+        __syncwarp();
+      }
     }
-  } else if (warp < 6) {
-    // ================================================================ converter group
-    const int quad = warp & 3;  // TMEM lane quadrant this warp may access
+  } else if (warp < 10) {
+    // ================================================================ converter groups A, B
+    const int half = (warp - 2) >> 2;  // column half this group owns
+    const int quad = warp & 3;         // TMEM lane quadrant this warp may access
     const int row = quad * 32 + lane;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
     const uint32_t sb_row = sb_addr + row * 128;
     const uint32_t swz = static_cast<uint32_t>(row & 7);
-    uint32_t r[32];
+    constexpr int SBLK = DV / 64;  // 32-column state blocks per group
+    uint32_t ra[32], rb[32];
 
     // Packs 32 fp32 state values (columns cb*32 ..) to bf16 and writes them to the B-operand
     // buffer: [dv group of 64][dk row][128 B], 16-byte pieces XOR-swizzled by (row % 8).
-    auto store_sb = [&](int cb) {
+    auto store_sb = [&](int cb, const uint32_t (&r)[32]) {
       const uint32_t grp = sb_row + (cb >> 1) * (DK * 128);
       const uint32_t j0 = (cb & 1) * 4;
 #pragma unroll
@@ -285,84 +366,111 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         ptx::st_shared_v4(grp + (((j0 + jj) ^ swz) << 4), a0, a1, a2, a3);
       }
     };
+    auto write_final = [&](int cb, const uint32_t (&r)[32]) {
+      if (row < p.st_rows) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (cb * 32 + j < p.st_cols) pr.s_final[st_off(row, cb * 32 + j)] = __uint_as_float(r[j]);
+      }
+    };
+    // Reads this group's share of S from TMEM and routes it to the operand buffer and/or s_final.
+    auto convert_state = [&](bool to_sb, bool to_final) {
+      if (SBLK == 2) {
+        ptx::tmem_ld32(lane_base + cfg::S_COL + (half * 2) * 32, ra);
+        ptx::tmem_ld32(lane_base + cfg::S_COL + (half * 2 + 1) * 32, rb);
+        ptx::tc_wait_ld();
+        if (to_final) { write_final(half * 2, ra); write_final(half * 2 + 1, rb); }
+        if (to_sb && row < DK) { store_sb(half * 2, ra); store_sb(half * 2 + 1, rb); }
+      } else {
+        ptx::tmem_ld32(lane_base + cfg::S_COL + half * 32, ra);
+        ptx::tc_wait_ld();
+        if (to_final) write_final(half, ra);
+        if (to_sb && row < DK) store_sb(half, ra);
+      }
+    };
 
     if (has_init) {
       const float* src = pr.s_init;
 #pragma unroll 1
-      for (int cb = 0; cb < DV / 32; ++cb) {
+      for (int jb = 0; jb < SBLK; ++jb) {
+        const int cb = half * SBLK + jb;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int col = cb * 32 + j;
           float x = 0.f;
           if (row < p.st_rows && col < p.st_cols) x = src[st_off(row, col)];
-          r[j] = __float_as_uint(x);
+          ra[j] = __float_as_uint(x);
         }
-        ptx::tmem_st32(lane_base + cfg::S_COL + cb * 32, r);
-        if (row < DK) store_sb(cb);
+        ptx::tmem_st32(lane_base + cfg::S_COL + cb * 32, ra);
+        if (row < DK) store_sb(cb, ra);
       }
       ptx::tc_wait_st();
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before();
-      ptx::mbar_arrive(sb_ready);
+      ptx::mbar_arrive(qs_ready);
     }
 
     if (mode == 0) {
       for (int i = 0; i < n_iter; ++i) {
-        // ---------------- P: fp32 -> causal mask -> bf16 A operand
+        // ---------------- P: fp32 -> causal mask -> bf16 A operand (this group's 64 columns)
+        if (warp == 2) FLA_TRACE_EVENT(10, i);
         int ok = ptx::mbar_wait(p_full, i & 1, abort_flag) ? 1 : 0;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        if (warp == 2) FLA_TRACE_EVENT(11, i);
         ptx::tc_fence_after();
+        // Column blocks of 32: relative to this warp's 32 rows a block is entirely kept, entirely
+        // masked, or (block index == quadrant) the diagonal block that needs per-element tests.
+        uint32_t pk[16];
 #pragma unroll
-        for (int cb = 0; cb < 4; ++cb) {
-          uint32_t pk[16];
-          const bool all_masked = reverse ? (cb < quad) : (cb > quad);  // warp-uniform
-          if (!all_masked) {
-            ptx::tmem_ld32(lane_base + cfg::P_COL + cb * 32, r);
-            ptx::tc_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int c0 = cb * 32 + 2 * j;
-              const bool k0 = reverse ? (c0 >= row) : (c0 <= row);
-              const bool k1 = reverse ? (c0 + 1 >= row) : (c0 + 1 <= row);
-              pk[j] = ptx::pack_bf16x2(k0 ? __uint_as_float(r[2 * j]) : 0.f,
-                                       k1 ? __uint_as_float(r[2 * j + 1]) : 0.f);
-            }
-          } else {
+        for (int jb = 0; jb < 2; ++jb) {
+          const int cb = half * 2 + jb;
+          const bool masked = reverse ? (cb < quad) : (cb > quad);  // warp-uniform
+          if (masked) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) pk[j] = 0u;
+          } else {
+            ptx::tmem_ld32(lane_base + cfg::P_COL + cb * 32, ra);
+            ptx::tc_wait_ld();
+            if (cb == quad) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const bool k0 = reverse ? (2 * j >= lane) : (2 * j <= lane);
+                const bool k1 = reverse ? (2 * j + 1 >= lane) : (2 * j + 1 <= lane);
+                pk[j] = ptx::pack_bf16x2(k0 ? __uint_as_float(ra[2 * j]) : 0.f,
+                                         k1 ? __uint_as_float(ra[2 * j + 1]) : 0.f);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                pk[j] = ptx::pack_bf16x2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1]));
+            }
           }
           ptx::tmem_st16(lane_base + cfg::PB_COL + cb * 16, pk);
         }
+        if (warp == 2) FLA_TRACE_EVENT(12, i);
         ptx::tc_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive(pb_ready);
+        if (warp == 2) FLA_TRACE_EVENT(13, i);
 
         // ---------------- S: fp32 -> bf16 B operand for the next chunk (or -> s_final)
         const bool last = (i == n_iter - 1);
-        const bool write_final = last && (pr.s_final != nullptr) && (g == nseg - 1);
-        if (!last || write_final) {
+        const bool to_final = last && (pr.s_final != nullptr) && (g == nseg - 1);
+        if (!last || to_final) {
           ok = ptx::mbar_wait(s_full, i & 1, abort_flag) ? 1 : 0;
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
+          if (warp == 2) FLA_TRACE_EVENT(14, i);
           ptx::tc_fence_after();
-#pragma unroll 1
-          for (int cb = 0; cb < DV / 32; ++cb) {
-            ptx::tmem_ld32(lane_base + cfg::S_COL + cb * 32, r);
-            ptx::tc_wait_ld();
-            if (write_final && row < p.st_rows) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (cb * 32 + j < p.st_cols)
-                  pr.s_final[st_off(row, cb * 32 + j)] = __uint_as_float(r[j]);
-            }
-            if (!last && row < DK) store_sb(cb);
-          }
+          convert_state(!last, to_final);
+          if (warp == 2) FLA_TRACE_EVENT(15, i);
           if (!last) {
             ptx::fence_proxy_async_smem();
             ptx::tc_fence_before();
-            ptx::mbar_arrive(sb_ready);
+            ptx::mbar_arrive(qs_ready);
           }
+          if (warp == 2) FLA_TRACE_EVENT(16, i);
         }
       }
     } else {
@@ -371,17 +479,7 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       ok = __all_sync(0xffffffffu, ok);
       if (ok && pr.s_final != nullptr) {
         ptx::tc_fence_after();
-#pragma unroll 1
-        for (int cb = 0; cb < DV / 32; ++cb) {
-          ptx::tmem_ld32(lane_base + cfg::S_COL + cb * 32, r);
-          ptx::tc_wait_ld();
-          if (row < p.st_rows) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (cb * 32 + j < p.st_cols)
-                pr.s_final[st_off(row, cb * 32 + j)] = __uint_as_float(r[j]);
-          }
-        }
+        convert_state(false, true);
       }
     }
   } else {
@@ -391,28 +489,42 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       const int row = quad * 32 + lane;
       const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
       const uint32_t swz = static_cast<uint32_t>(row & 7);
-      uint32_t r[32];
+      const bool leader = (threadIdx.x == 10 * 32);
+      uint32_t ra[32], rb[32];
       uint32_t pk[DV / 2];
+      // With an initial state the first "state ready" phase has no drained accumulator to wait
+      // for; the epilogue's share of that phase is given here.
+      if (has_init) ptx::mbar_arrive(qs_ready);
       for (int i = 0; i < n_iter; ++i) {
-        const int s = i % NS;
+        if (warp == 10) FLA_TRACE_EVENT(20, i);
         int ok = ptx::mbar_wait(o_full, i & 1, abort_flag) ? 1 : 0;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        if (warp == 10) FLA_TRACE_EVENT(21, i);
         ptx::tc_fence_after();
 #pragma unroll
-        for (int cb = 0; cb < DV / 32; ++cb) {
-          ptx::tmem_ld32(lane_base + cfg::O_COL + cb * 32, r);
+        for (int cb = 0; cb < DV / 32; cb += 2) {
+          ptx::tmem_ld32(lane_base + cfg::O_COL + cb * 32, ra);
+          ptx::tmem_ld32(lane_base + cfg::O_COL + (cb + 1) * 32, rb);
           ptx::tc_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
+          for (int j = 0; j < 16; ++j) {
             pk[cb * 16 + j] =
-                ptx::pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                ptx::pack_bf16x2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1]));
+            pk[(cb + 1) * 16 + j] =
+                ptx::pack_bf16x2(__uint_as_float(rb[2 * j]), __uint_as_float(rb[2 * j + 1]));
+          }
         }
         ptx::tc_fence_before();
-        ptx::mbar_arrive(o_free);
-        // Stage O in this chunk's Q buffer (every MMA that read it has completed), same
-        // swizzled layout as the loads, and hand it to the TMA store.
-        const uint32_t obuf = stage_addr(s) + row * 128;
+        ptx::mbar_arrive(qs_ready);
+        if (warp == 10) FLA_TRACE_EVENT(22, i);
+        // The staging buffer is free once the previous chunk's TMA store has read it.
+        if (i > 0) {
+          ok = ptx::mbar_wait(ost_free, (i - 1) & 1, abort_flag) ? 1 : 0;
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+        const uint32_t obuf = ost_addr + row * 128;
 #pragma unroll
         for (int gg = 0; gg < cfg::GV; ++gg) {
 #pragma unroll
@@ -424,18 +536,21 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         }
         ptx::fence_proxy_async_smem();
         ptx::mbar_arrive(o_staged);
+        if (warp == 10) FLA_TRACE_EVENT(23, i);
         // One thread waits (bounded) until all 128 rows are staged, then issues the store.
-        if (threadIdx.x == 6 * 32 && ptx::mbar_wait(o_staged, i & 1, abort_flag)) {
+        if (leader && ptx::mbar_wait(o_staged, i & 1, abort_flag)) {
           const int tok = mem_chunk(i) * kChunk;
 #pragma unroll
           for (int gg = 0; gg < cfg::GV; ++gg)
-            ptx::tma_store_4d(&pr.o, stage_addr(s) + gg * kGroupBytes, gg * 64, tok, h, b);
+            ptx::tma_store_4d(&pr.o, ost_addr + gg * kGroupBytes, gg * 64, tok, h, b);
           ptx::bulk_commit_group();
+          FLA_TRACE_EVENT(24, i);
           ptx::bulk_wait_group_read0();
-          ptx::mbar_arrive(empty_bar(s));
+          ptx::mbar_arrive(ost_free);
+          FLA_TRACE_EVENT(25, i);
         }
       }
-      if (threadIdx.x == 6 * 32) ptx::bulk_wait_group0();
+      if (leader) ptx::bulk_wait_group0();
     }
   }
 
