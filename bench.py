@@ -79,7 +79,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "50", "-i", str(self.index)],
+                 "-lms", "20", "-i", str(self.index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -190,7 +190,7 @@ def run_reference(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
@@ -237,11 +237,16 @@ def main():
             torch.cuda.synchronize(device)
 
     # ---------------------------------------------------------------- kernel-level timing
+    # The forward also writes its final state (fp32, batch*heads x dk x dv) when the backward can
+    # use it to sweep q, k, v, dO once -- what LinearAttention.apply + backward do.
+    s_state = None
+    if ops.backward_uses_final_state(q, v):
+        s_state = torch.empty(Bl * Hl, dk, dv, dtype=torch.float32, device=device)
     launches = 0
     for _ in range(warmup):
-        ops.causal_dot_product_fwd(q, k, v)
+        ops.causal_dot_product_fwd(q, k, v, s_final=s_state)
         launches_f = lib.fla_sm100_last_launch_count()
-        ops.causal_dot_product_bwd(dy, q, k, v)
+        ops.causal_dot_product_bwd(dy, q, k, v, s_last=s_state)
         launches_b = lib.fla_sm100_last_launch_count()
     barrier()
     ops.check_status(device)
@@ -252,9 +257,9 @@ def main():
     barrier()
     for i in range(steps):
         ev[i][0].record(stream)
-        ops.causal_dot_product_fwd(q, k, v)
+        ops.causal_dot_product_fwd(q, k, v, s_final=s_state)
         ev[i][1].record(stream)
-        ops.causal_dot_product_bwd(dy, q, k, v)
+        ops.causal_dot_product_bwd(dy, q, k, v, s_last=s_state)
         ev[i][2].record(stream)
     barrier()
     clocks = sampler.stop() if rank == 0 else None

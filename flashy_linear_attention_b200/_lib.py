@@ -11,7 +11,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libflashlinear_sm100.so")
 
-FLA_ABI_VERSION = 1
+FLA_ABI_VERSION = 2
 
 
 class FlaTensor(ctypes.Structure):
@@ -42,6 +42,7 @@ class FlaArgs(ctypes.Structure):
         ("s_final", ctypes.c_void_p),
         ("r_init", ctypes.c_void_p),
         ("r_final", ctypes.c_void_p),
+        ("s_last", ctypes.c_void_p),
         ("segments", ctypes.c_int32),
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_size_t),

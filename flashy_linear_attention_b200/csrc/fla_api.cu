@@ -98,7 +98,7 @@ int encode_map(CUtensorMap* m, const Operand& o, int B, int H, int N) {
 // One product out_i = sum (a_i . b_j) c_j; a, b have dim `da`, c and out have dim `dc`.
 struct Product {
   Operand a, b, c, out;
-  int reverse;
+  int flags;  // fla::kFlag* bits
   const float* ext_init;  // caller's running state, or null
   float* ext_final;
   int ext_trans;  // the caller's state arrays hold the transpose of the product's [da][dc] state
@@ -259,7 +259,7 @@ int run_products(const Product* prods, int nprob, int B, int H, int N, int da, i
     if ((rc = encode_map(&pr.q, pd.a, B, H, N)) || (rc = encode_map(&pr.k, pd.b, B, H, N)) ||
         (rc = encode_map(&pr.v, pd.c, B, H, N)) || (rc = encode_map(&pr.o, pd.out, B, H, N)))
       return rc;
-    pr.reverse = pd.reverse;
+    pr.flags = pd.flags;
     want_final |= (pd.ext_final != nullptr);
   }
 
@@ -430,7 +430,7 @@ int fla_sm100_fwd(const FlaArgs* a) {
   p.b = operand(a->k, a->dk);
   p.c = operand(a->v, a->dv);
   p.out = operand(a->o, a->dv);
-  p.reverse = 0;
+  p.flags = 0;
   p.ext_init = a->s_init;
   p.ext_final = a->s_final;
   p.ext_trans = 0;
@@ -451,7 +451,7 @@ int fla_sm100_bwd(const FlaArgs* a) {
   pq.b = operand(a->v, a->dv);
   pq.c = operand(a->k, a->dk);
   pq.out = operand(a->d_q, a->dk);
-  pq.reverse = 0;
+  pq.flags = 0;
   pq.ext_init = a->s_init;
   pq.ext_final = nullptr;
   pq.ext_trans = 1;
@@ -461,7 +461,7 @@ int fla_sm100_bwd(const FlaArgs* a) {
   pv.b = operand(a->q, a->dk);
   pv.c = operand(a->d_o, a->dv);
   pv.out = operand(a->d_v, a->dv);
-  pv.reverse = 1;
+  pv.flags = fla::kFlagDescending | fla::kFlagUpperMask;
   pv.ext_init = a->r_init;
   pv.ext_final = a->r_final;
   pv.ext_trans = 0;
@@ -471,7 +471,7 @@ int fla_sm100_bwd(const FlaArgs* a) {
   pk.b = operand(a->d_o, a->dv);
   pk.c = operand(a->q, a->dk);
   pk.out = operand(a->d_k, a->dk);
-  pk.reverse = 1;
+  pk.flags = fla::kFlagDescending | fla::kFlagUpperMask;
   pk.ext_init = a->r_init;
   pk.ext_final = nullptr;
   pk.ext_trans = 1;
@@ -479,6 +479,15 @@ int fla_sm100_bwd(const FlaArgs* a) {
   const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
   int nseg = a->segments > 0 ? a->segments
                              : auto_segments(3, a->batch * a->heads, nchunks, dev->sm_count);
+  if (nseg > nchunks) nseg = nchunks;
+  if (a->s_last != nullptr && nseg <= 1) {
+    // The forward state after this call's tokens is known: dQ can walk the sequence in the same
+    // descending order as dV and dK (state = total minus suffix), so the three products of a
+    // head stream the same chunks at the same time and share their q, k, v, dO reads in L2.
+    pq.flags = fla::kFlagDescending | fla::kFlagTotalMinusSuffix;
+    if (a->s_init == nullptr) pq.flags |= fla::kFlagFirstChunkExact;  // nothing precedes token 0
+    pq.ext_init = a->s_last;
+  }
   if (a->dk == a->dv) {
     // Same shapes: one grid. Block x = product; dV and dK of a head are neighbours in launch order.
     Product all[3] = {pq, pv, pk};

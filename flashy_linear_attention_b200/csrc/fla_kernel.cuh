@@ -1,8 +1,8 @@
 // Chunked causal linear attention for sm_100a.
 //
 // One generic kernel computes, for one head and one run of 128-token chunks,
-//     o_i = sum_{j <= i} (q_i . k_j) v_j            (reverse = 0)
-//     o_i = sum_{j >= i} (q_i . k_j) v_j            (reverse = 1)
+//     o_i = sum_{j <= i} (q_i . k_j) v_j            (causal)
+//     o_i = sum_{j >= i} (q_i . k_j) v_j            (anti-causal: descending walk, upper mask)
 // as  P = (Q K^T) (.) mask,  O = P V + Q S,  S += K^T V   per chunk, where S (dk x dv, fp32) is the
 // running state carried in tensor memory. The forward pass and all three gradients are this same
 // product with the operands permuted (see fla_api.cu), which replaces the quadratic tile loops of
@@ -33,9 +33,23 @@ struct Problem {
   CUtensorMap q, k, v, o;  // 4-D maps (dim, token, head, batch), box 64 x 128 x 1 x 1, 128B swizzle
   const float* s_init;     // [bh * segments + g][st_rows][st_cols] fp32, or null
   float* s_final;          // same indexing, or null
-  int reverse;
+  int flags;               // kFlag* bits below
   int st_trans;            // state arrays are stored transposed: element (row, col) at [col][row]
 };
+
+// Problem::flags
+constexpr int kFlagDescending = 1;  // walk the chunks from the last token to the first
+constexpr int kFlagUpperMask = 2;   // keep (a_i . b_j) for j >= i instead of j <= i
+// "Total minus suffix" form of the causal (j <= i) sum for a descending walk: the state starts as
+// the sum over ALL tokens (s_init), every chunk SUBTRACTS its b^T c after using the state, and the
+// intra-chunk tile contributes -(a_i . b_j) for j > i, because the state a chunk sees still
+// contains that chunk's own tokens:  sum_{j<=i} = sum_{j in chunks <= this one} - sum_{j>i, same chunk}.
+constexpr int kFlagTotalMinusSuffix = 4;
+// With kFlagTotalMinusSuffix: the sequence has no tokens before token 0 of this call, so the state
+// seen by the first chunk is exactly that chunk's own sum. That chunk is then computed from its
+// score tile alone (ordinary lower mask, no state term); otherwise its first rows would be the
+// small difference of two 128-term sums and lose accuracy.
+constexpr int kFlagFirstChunkExact = 8;
 
 struct KernelParams {
   Problem prob[3];
@@ -135,7 +149,10 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
   const int b = bh / p.heads;
   const int chunk0 = g * p.seg_chunks;
   const int n_iter = min(p.seg_chunks, p.nchunks - chunk0);
-  const bool reverse = pr.reverse != 0;
+  const bool descending = (pr.flags & kFlagDescending) != 0;
+  const bool tms = (pr.flags & kFlagTotalMinusSuffix) != 0;
+  const bool upper_flag = (pr.flags & kFlagUpperMask) != 0;
+  const bool exact0 = tms && (pr.flags & kFlagFirstChunkExact) != 0;
   const bool has_init = (mode == 0) && (pr.s_init != nullptr);
   const size_t st_elems = static_cast<size_t>(p.st_rows) * p.st_cols;
   const size_t st_index = (static_cast<size_t>(bh) * nseg + g) * st_elems;
@@ -188,7 +205,11 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
     const int ok = ptx::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
     return __all_sync(0xffffffffu, ok) != 0;
   };
-  auto mem_chunk = [&](int i) { return reverse ? (p.nchunks - 1 - (chunk0 + i)) : (chunk0 + i); };
+  auto mem_chunk = [&](int i) {
+    return descending ? (p.nchunks - 1 - (chunk0 + i)) : (chunk0 + i);
+  };
+  // chunk i is computed without the state (see kFlagFirstChunkExact)
+  auto plain_chunk = [&](int i) { return exact0 && mem_chunk(i) == 0; };
   auto slot_addr = [&](int t) {
     return smem_base + static_cast<uint32_t>(t % NSLOT) * cfg::TILE_BYTES;
   };
@@ -230,7 +251,9 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
     constexpr uint32_t IDESC_QK = ptx::make_idesc(128, kChunk, false, false);  // P  = Q K^T
     constexpr uint32_t IDESC_PV = ptx::make_idesc(128, DV, false, true);       // O += Pb V
     constexpr uint32_t IDESC_QS = ptx::make_idesc(128, DV, false, true);       // O  = Q Sb
-    constexpr uint32_t IDESC_KV = ptx::make_idesc(128, DV, true, true);        // S += K^T V
+    constexpr uint32_t IDESC_KV_ADD = ptx::make_idesc(128, DV, true, true);    // S += K^T V
+    constexpr uint32_t IDESC_KV_SUB = IDESC_KV_ADD | (1u << 13);               // S -= K^T V (A negated)
+    const uint32_t IDESC_KV = tms ? IDESC_KV_SUB : IDESC_KV_ADD;
     const uint32_t tP = tmem_base + cfg::P_COL;
     const uint32_t tPb = tmem_base + cfg::PB_COL;
     const uint32_t tO = tmem_base + cfg::O_COL;
@@ -268,7 +291,9 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         const uint32_t v_lo = ptx::desc_lo(slot_addr(3 * i + 2), kGroupBytes);
         const uint32_t sb_lo = ptx::desc_lo(sb_addr, DK * 128);
         const bool have_state = (i > 0) || has_init;
-        const uint32_t acc0 = have_state ? 1u : 0u;
+        const bool use_state = have_state && !plain_chunk(i);
+        const uint32_t acc0 = have_state ? 1u : 0u;   // S accumulates
+        const uint32_t acc_o = use_state ? 1u : 0u;   // O already holds Q Sb
         FLA_TRACE_EVENT(0, i);
         // ---- O = Q Sb  (inter-chunk part; Sb is dk x dv, dv contiguous: MN-major B). Needs the
         // converted state of the previous chunk and the O accumulator drained by the epilogue.
@@ -277,7 +302,7 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
           ++qs_waits;
           FLA_TRACE_EVENT(2, i);
           ptx::tc_fence_after();
-          if (leader) {
+          if (leader && use_state) {
 #pragma unroll
             for (int kk = 0; kk < DK / 16; ++kk) {
               const uint32_t off = ((kk >> 2) * kGroupBytes + (kk & 3) * 32) >> 4;
@@ -312,7 +337,7 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
 #pragma unroll
           for (int kk = 0; kk < kChunk / 16; ++kk) {
             ptx::mma_ts(tO, tPb + kk * 8, v_lo + kk * (2048 >> 4), ptx::kDescHi, IDESC_PV,
-                        kk > 0 ? 1u : acc0);
+                        kk > 0 ? 1u : acc_o);
           }
           ptx::tc_commit(o_full);
         }
@@ -422,10 +447,12 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         // Column blocks of 32: relative to this warp's 32 rows a block is entirely kept, entirely
         // masked, or (block index == quadrant) the diagonal block that needs per-element tests.
         uint32_t pk[16];
+        const bool tms_i = tms && !plain_chunk(i);     // subtract the strictly upper part
+        const bool upper = tms_i || upper_flag;         // which side of the diagonal is kept
 #pragma unroll
         for (int jb = 0; jb < 2; ++jb) {
           const int cb = half * 2 + jb;
-          const bool masked = reverse ? (cb < quad) : (cb > quad);  // warp-uniform
+          const bool masked = upper ? (cb < quad) : (cb > quad);  // warp-uniform
           if (masked) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) pk[j] = 0u;
@@ -433,10 +460,12 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
             ptx::tmem_ld32(lane_base + cfg::P_COL + cb * 32, ra);
             ptx::tc_wait_ld();
             if (cb == quad) {
+              // first kept column (upper) resp. last kept column (lower) of this thread's row
+              const int edge = tms_i ? lane + 1 : lane;
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
-                const bool k0 = reverse ? (2 * j >= lane) : (2 * j <= lane);
-                const bool k1 = reverse ? (2 * j + 1 >= lane) : (2 * j + 1 <= lane);
+                const bool k0 = upper ? (2 * j >= edge) : (2 * j <= edge);
+                const bool k1 = upper ? (2 * j + 1 >= edge) : (2 * j + 1 <= edge);
                 pk[j] = ptx::pack_bf16x2(k0 ? __uint_as_float(ra[2 * j]) : 0.f,
                                          k1 ? __uint_as_float(ra[2 * j + 1]) : 0.f);
               }
@@ -444,6 +473,10 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
 #pragma unroll
               for (int j = 0; j < 16; ++j)
                 pk[j] = ptx::pack_bf16x2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1]));
+            }
+            if (tms_i) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) pk[j] ^= 0x80008000u;  // negate both halves
             }
           }
           ptx::tmem_st16(lane_base + cfg::PB_COL + cb * 16, pk);

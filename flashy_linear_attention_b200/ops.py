@@ -180,8 +180,12 @@ def causal_dot_product_bwd(
     r_init: Optional[torch.Tensor] = None,
     r_final: Optional[torch.Tensor] = None,
     segments: int = 0,
+    s_last: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Gradients (dQ, dK, dV) of causal_dot_product_fwd for upstream gradient `grad_output`."""
+    """Gradients (dQ, dK, dV) of causal_dot_product_fwd for upstream gradient `grad_output`.
+
+    s_last (optional) is the forward state after these tokens, i.e. what the forward call wrote to
+    `s_final`; with it the backward reads q, k, v, dO from HBM only once."""
     _check_inputs(grad_output, q, k, v)
     B, H, N, dk = q.shape
     dv = v.shape[-1]
@@ -196,12 +200,23 @@ def causal_dot_product_bwd(
     a.s_init = _fptr(s_init, "s_init", (B * H, dk, dv))
     a.r_init = _fptr(r_init, "r_init", (B * H, dk, dv))
     a.r_final = _fptr(r_final, "r_final", (B * H, dk, dv))
+    a.s_last = _fptr(s_last, "s_last", (B * H, dk, dv))
     a.segments = segments
     _call(1, a, q.device)
     for full, view in ((dQ, dQv), (dK, dKv), (dV, dVv)):
         if view is not full:
             full.copy_(view)
     return dQ, dK, dV
+
+
+def backward_uses_final_state(q: torch.Tensor, v: torch.Tensor) -> bool:
+    """True when the backward of this shape runs unsegmented, i.e. can take the forward's final
+    state (`s_last`) and sweep q, k, v, dO once for all three gradients."""
+    B, H, N, dk = q.shape
+    a = FlaArgs()
+    a.batch, a.heads, a.seqlen, a.dk, a.dv = B, H, N, dk, v.shape[-1]
+    with torch.cuda.device(q.device):
+        return _lib.load().fla_sm100_auto_segments(ctypes.byref(a), 1) <= 1
 
 
 def chunk_state(b: torch.Tensor, c: torch.Tensor, segments: int = 0) -> torch.Tensor:
@@ -236,10 +251,20 @@ def _assert_shapes(hd_qk: int, sq: int) -> None:
     ), f"Number of elements in sequence must be a multiple of {block_sq}, {sq, block_sq}"
 
 
+def check_forward_preconditions(q: torch.Tensor, v: torch.Tensor, smallv: bool) -> None:
+    """The AssertionErrors of linear_flash_wrapper_fwd / linear_flash_wrapper_fwd_smallv_hd."""
+    hd_qk, sq, hd_v = q.shape[-1], q.shape[-2], v.shape[-1]
+    if smallv:
+        assert _next_pow2(hd_v) == hd_v, "Expected value head dimension to be a power of 2."
+        assert _next_pow2(hd_v) <= _next_pow2(
+            hd_qk
+        ), "Value head dimension must be less than Query/Key head dimension."
+    _assert_shapes(hd_qk, sq)
+
+
 def linear_flash_wrapper_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     """Causal linear attention forward, dk == dv (linear_attn_kernels.py:310-341)."""
-    batch, nh, sq, hd = q.shape
-    _assert_shapes(hd, sq)
+    check_forward_preconditions(q, v, smallv=False)
     return causal_dot_product_fwd(q, k, v)
 
 
@@ -256,13 +281,7 @@ def linear_flash_wrapper_fwd_smallv_hd(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
 ) -> torch.Tensor:
     """Forward with separate q/k and v head dims (linear_attn_kernels_smallv_hd.py:320-359)."""
-    batch, nh, sq, hd_qk = q.shape
-    hd_v = v.shape[-1]
-    assert _next_pow2(hd_v) == hd_v, "Expected value head dimension to be a power of 2."
-    assert _next_pow2(hd_v) <= _next_pow2(
-        hd_qk
-    ), "Value head dimension must be less than Query/Key head dimension."
-    _assert_shapes(hd_qk, sq)
+    check_forward_preconditions(q, v, smallv=True)
     return causal_dot_product_fwd(q, k, v)
 
 

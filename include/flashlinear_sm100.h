@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define FLA_ABI_VERSION 1
+#define FLA_ABI_VERSION 2
 
 enum {
   FLA_OK = 0,
@@ -72,6 +72,11 @@ typedef struct FlaArgs {
   float* s_final;
   const float* r_init;
   float* r_final;
+  /* Backward only, optional: the forward state AFTER this call's tokens (what the forward call
+   * wrote to s_final). When given (and the call is not split into segments) dQ is computed in the
+   * same end-to-start sweep as dK and dV, which lets the three share every read of q, k, v, dO;
+   * s_init is then not needed. */
+  const float* s_last;
 
   /* Sequence segments per head (intra-GPU sequence split). 0 = pick automatically, 1 = none.
    * With more than one segment the call needs fla_sm100_workspace_bytes() of scratch. */

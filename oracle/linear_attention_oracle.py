@@ -159,6 +159,35 @@ def causal_product_chunked(a, b, c, chunk=128, reverse=False, s_init=None, emula
     return out, s
 
 
+def causal_product_total_minus_suffix(a, b, c, total, chunk=128, first_chunk_exact=True, emulate_bf16=False):
+    """The causal sum out_i = sum_{j<=i} (a_i . b_j) c_j walked from the LAST chunk to the first,
+    as the CUDA kernels do for dQ when the forward's final state is known: the state starts as
+    `total` = sum over all tokens of b^T c, a chunk uses it while it still contains the chunk's own
+    tokens and corrects with the strictly upper part of its score tile,
+        O = A S_incl - (strict_upper(A B^T)) C ;  S_incl -= B^T C,
+    except for the chunk that starts the sequence (first_chunk_exact), which has no prefix and is
+    computed from its lower-masked score tile alone."""
+    a, b, c = (np.asarray(t) for t in (a, b, c))
+    dt = np.float32 if emulate_bf16 else np.result_type(a.dtype, np.float32)
+    a, b, c = a.astype(dt), b.astype(dt), c.astype(dt)
+    n = a.shape[-2]
+    out = np.zeros(a.shape[:-1] + (c.shape[-1],), dtype=dt)
+    s = np.array(total, dtype=dt).reshape(a.shape[:-2] + (a.shape[-1], c.shape[-1]))
+    rnd = bf16_round if emulate_bf16 else (lambda x: x)
+    for ci in range((n + chunk - 1) // chunk - 1, -1, -1):
+        lo, hi = ci * chunk, min((ci + 1) * chunk, n)
+        ac, bc, cc = a[..., lo:hi, :], b[..., lo:hi, :], c[..., lo:hi, :]
+        m = hi - lo
+        scores = np.matmul(ac, np.swapaxes(bc, -1, -2))
+        if ci == 0 and first_chunk_exact:
+            o = np.matmul(rnd(scores * np.tril(np.ones((m, m), dtype=dt))), cc)
+        else:
+            o = np.matmul(rnd(-scores * np.triu(np.ones((m, m), dtype=dt), 1)), cc) + np.matmul(ac, rnd(s))
+        out[..., lo:hi, :] = rnd(o)
+        s = s - np.matmul(np.swapaxes(bc, -1, -2), cc)
+    return out
+
+
 def chunked_fwd(q, k, v, chunk=128, s_init=None, emulate_bf16=False):
     """Forward: (out, S_final) with S = sum k^T v."""
     return causal_product_chunked(q, k, v, chunk, False, s_init, emulate_bf16)

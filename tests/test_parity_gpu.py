@@ -149,6 +149,30 @@ def test_segmented_equals_oracle(segments):
     _run_and_check(q, k, v, dy, segments=segments)
 
 
+@pytest.mark.parametrize("shape", [(1, 1, 128, 128, 128), (2, 2, 576, 64, 64), (1, 3, 1024, 128, 128), (1, 2, 320, 96, 32)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_single_sweep_backward_with_forward_state(shape):
+    """Backward given the forward's final state (s_last): dQ is computed in the same descending
+    sweep as dK, dV from "total minus suffix" states. Same tolerance as the ordinary backward."""
+    ops = _ops()
+    B, H, N, dk, dv = shape
+    rng = np.random.default_rng(N + dk)
+    q = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, dk)).astype(np.float32)))
+    k = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, dk)).astype(np.float32)))
+    v = orc.bf16_round(rng.standard_normal((B, H, N, dv)).astype(np.float32))
+    dy = orc.bf16_round(rng.standard_normal((B, H, N, dv)).astype(np.float32))
+    tq, tk, tv, tdy = (_to_dev(t) for t in (q, k, v, dy))
+    s_state = torch.empty(B * H, dk, dv, dtype=torch.float32, device=DEV)
+    ops.causal_dot_product_fwd(tq, tk, tv, s_final=s_state, segments=1)
+    dq, dk_, dv_ = ops.causal_dot_product_bwd(tdy, tq, tk, tv, s_last=s_state, segments=1)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    rq, rk, rv = orc.linear_ref_grads(*(t.astype(np.float64) for t in (q, k, v, dy)))
+    _check("dq", _np(dq), rq)
+    _check("dk", _np(dk_), rk)
+    _check("dv", _np(dv_), rv)
+
+
 def test_kernel_rounding_matches_emulated_rounding_tightly():
     """Against the oracle's emulation of the kernel's own rounding points the difference is only
     summation order inside the MMAs: far below the bf16 tolerance."""
@@ -275,9 +299,14 @@ def test_full_size_properties(cfg):
     seg = ops.causal_dot_product_fwd(q, k, v, segments=4)
     assert (torch.linalg.norm(seg.float() - out.float()) / torch.linalg.norm(out.float())).item() < 2e-3
     dy = torch.randn(B, H, N, d, device=DEV, generator=gen).to(torch.bfloat16)
-    dq, dk, dv = ops.causal_dot_product_bwd(dy, q, k, v)
+    s_state = torch.empty(B * H, d, d, dtype=torch.float32, device=DEV)
+    ops.causal_dot_product_fwd(q, k, v, s_final=s_state)
+    dq, dk, dv = ops.causal_dot_product_bwd(dy, q, k, v, s_last=s_state)   # single-sweep form
+    dq2, dk2, dv2 = ops.causal_dot_product_bwd(dy, q, k, v)                # two-direction form
     torch.cuda.synchronize()
     ops.check_status(DEV)
+    assert (torch.linalg.norm(dq.float() - dq2.float()) / torch.linalg.norm(dq2.float())).item() < FROB_TOL
+    assert torch.equal(dk, dk2) and torch.equal(dv, dv2)
     # one head, full length, against the oracle (naive O(N^2) path on the CPU)
     b, h = B - 1, H - 1
     qs, ks, vs, dys = (_np(t[b, h]).astype(np.float64) for t in (q, k, v, dy))
