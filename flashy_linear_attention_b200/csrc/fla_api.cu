@@ -69,15 +69,15 @@ Operand operand(const FlaTensor& t, int dim) {
 int check_operand(const Operand& o, int B, int H) {
   if (o.ptr == nullptr) return FLA_ERR_INVALID;
   if (reinterpret_cast<uintptr_t>(o.ptr) % 16 != 0) return FLA_ERR_ALIGNMENT;
-  if ((o.sn * 2) % 16 != 0 || o.sn < o.dim) return FLA_ERR_ALIGNMENT;
+  if ((o.sn * 2) % 16 != 0 || o.sn < (o.dim + 7) / 8 * 8) return FLA_ERR_ALIGNMENT;
   if (H > 1 && (o.sh * 2) % 16 != 0) return FLA_ERR_ALIGNMENT;
   if (B > 1 && (o.sb * 2) % 16 != 0) return FLA_ERR_ALIGNMENT;
   return FLA_OK;
 }
 
-// 4-D tensor map (dim, token, head, batch); box = 64 columns x 128 tokens, 128-byte swizzle.
+// 4-D tensor map (dim, token, head, batch); box = 64 columns x box_rows tokens, 128-byte swizzle.
 // Columns >= dim and tokens >= N are out of bounds: loads fill zeros, stores skip them.
-int encode_map(CUtensorMap* m, const Operand& o, int B, int H, int N) {
+int encode_map(CUtensorMap* m, const Operand& o, int B, int H, int N, int box_rows = fla::kChunk) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return FLA_ERR_CUDA;
   const cuuint64_t row_bytes = static_cast<cuuint64_t>(o.sn) * 2;
@@ -87,7 +87,7 @@ int encode_map(CUtensorMap* m, const Operand& o, int B, int H, int N) {
   cuuint64_t sh = (H > 1) ? static_cast<cuuint64_t>(o.sh) * 2 : row_bytes * N;
   cuuint64_t sb = (B > 1) ? static_cast<cuuint64_t>(o.sb) * 2 : sh * H;
   cuuint64_t strides[3] = {row_bytes, sh, sb};
-  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(fla::kChunk), 1, 1};
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(o.ptr), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -257,9 +257,10 @@ int run_products(const Product* prods, int nprob, int B, int H, int N, int da, i
       return rc;
     Problem& pr = kp.prob[i];
     if ((rc = encode_map(&pr.q, pd.a, B, H, N)) || (rc = encode_map(&pr.k, pd.b, B, H, N)) ||
-        (rc = encode_map(&pr.v, pd.c, B, H, N)) || (rc = encode_map(&pr.o, pd.out, B, H, N)))
+        (rc = encode_map(&pr.v, pd.c, B, H, N)) || (rc = encode_map(&pr.o, pd.out, B, H, N, 32)))
       return rc;
     pr.flags = pd.flags;
+    pr.n_tokens = N;
     want_final |= (pd.ext_final != nullptr);
   }
 

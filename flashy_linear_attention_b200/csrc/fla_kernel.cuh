@@ -23,6 +23,8 @@
 #pragma once
 #include "ptx.cuh"
 
+#include <type_traits>
+
 namespace fla {
 
 constexpr int kChunk = 128;                // tokens per chunk (= MMA M)
@@ -30,11 +32,14 @@ constexpr int kThreads = 448;              // 14 warps
 constexpr int kGroupBytes = kChunk * 128;  // one 64-column group of a chunk tile: 128 rows x 128 B
 
 struct Problem {
-  CUtensorMap q, k, v, o;  // 4-D maps (dim, token, head, batch), box 64 x 128 x 1 x 1, 128B swizzle
+  CUtensorMap q, k, v;     // 4-D maps (dim, token, head, batch), box 64 x 128 x 1 x 1, 128B swizzle
+  CUtensorMap o;           // output map with a 64 x 32 box: every epilogue warp stores its own rows
   const float* s_init;     // [bh * segments + g][st_rows][st_cols] fp32, or null
   float* s_final;          // same indexing, or null
   int flags;               // kFlag* bits below
   int st_trans;            // state arrays are stored transposed: element (row, col) at [col][row]
+  int n_tokens;            // sequence length
+  int pad_;
 };
 
 // Problem::flags
@@ -96,12 +101,12 @@ struct Cfg {
   static_assert(NSLOT >= 5, "need at least five tile slots");
   static constexpr int SMEM_BYTES = 1024 + NSLOT * TILE_BYTES + SB_BYTES + OST_BYTES + BAR_BYTES;
   static_assert(SMEM_BYTES <= SMEM_LIMIT, "shared memory budget");
-  static_assert((2 * NSLOT + 8) * 8 + 16 <= BAR_BYTES, "barrier area");
+  static_assert((2 * NSLOT + 10) * 8 + 16 <= BAR_BYTES, "barrier area");
   // TMEM columns (32-bit each, 128 lanes)
-  static constexpr int P_COL = 0;         // P fp32: 128 columns
-  static constexpr int PB_COL = 128;      // P bf16 (two per column): 64 columns
-  static constexpr int O_COL = 192;       // O fp32: DV columns
-  static constexpr int S_COL = 192 + DV;  // S fp32: DV columns, lane = dk index
+  static constexpr int P_COL = 0;   // P fp32: 128 columns. Its bf16 form (two per column) is written
+                                    // in place: columns [0,32) for tokens 0-63, [64,96) for 64-127.
+  static constexpr int O_COL = 128;           // O fp32: two buffers of DV columns (even / odd chunk)
+  static constexpr int S_COL = 128 + 2 * DV;  // S fp32: DV columns, lane = dk index
   static constexpr int TMEM_COLS = 512;
   static_assert(S_COL + DV <= TMEM_COLS, "TMEM budget");
 };
@@ -134,13 +139,13 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
   auto empty_bar = [&](int s) { return bar_base + 8u * (NSLOT + s); };
   const uint32_t p_full = bar_base + 8u * (2 * NSLOT + 0);
   const uint32_t pb_ready = bar_base + 8u * (2 * NSLOT + 1);
-  const uint32_t o_full = bar_base + 8u * (2 * NSLOT + 2);
-  const uint32_t qs_ready = bar_base + 8u * (2 * NSLOT + 3);
+  const uint32_t o_full0 = bar_base + 8u * (2 * NSLOT + 2);  // buffer 1: o_full1
+  const uint32_t o_full1 = bar_base + 8u * (2 * NSLOT + 9);
+  const uint32_t sb_ready = bar_base + 8u * (2 * NSLOT + 3);
+  const uint32_t o_free0 = bar_base + 8u * (2 * NSLOT + 5);  // o_free0 + 8: buffer 1
   const uint32_t s_full = bar_base + 8u * (2 * NSLOT + 4);
-  const uint32_t o_staged = bar_base + 8u * (2 * NSLOT + 6);
-  const uint32_t ost_free = bar_base + 8u * (2 * NSLOT + 7);
   const uint32_t holder_off =
-      NSLOT * cfg::TILE_BYTES + cfg::SB_BYTES + cfg::OST_BYTES + 8u * (2 * NSLOT + 8);
+      NSLOT * cfg::TILE_BYTES + cfg::SB_BYTES + cfg::OST_BYTES + 8u * (2 * NSLOT + 10);
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_gen + holder_off);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + holder_off + 4);
 
@@ -174,11 +179,12 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
     }
     ptx::mbar_init(p_full, 1);
     ptx::mbar_init(pb_ready, 256);
-    ptx::mbar_init(o_full, 1);
-    ptx::mbar_init(qs_ready, 256 + 128);  // state converted (256) and O drained (128)
+    ptx::mbar_init(o_full0, 1);
+    ptx::mbar_init(o_full1, 1);
+    ptx::mbar_init(sb_ready, 256);
+    ptx::mbar_init(o_free0, 128);
+    ptx::mbar_init(o_free0 + 8, 128);
     ptx::mbar_init(s_full, 1);
-    ptx::mbar_init(o_staged, 128);
-    ptx::mbar_init(ost_free, 1);
     ptx::fence_barrier_init();
     ptx::fence_proxy_async_smem();
   }
@@ -202,8 +208,14 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
   // Wait executed by a whole warp; the outcome is made uniform so that the warp never diverges
   // around .sync.aligned instructions.
   auto wait_uniform = [&](uint32_t bar, uint32_t parity) {
+#ifdef FLA_WAIT_LANE0
+    int ok = 1;
+    if (lane == 0) ok = ptx::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+#else
     const int ok = ptx::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
     return __all_sync(0xffffffffu, ok) != 0;
+#endif
   };
   auto mem_chunk = [&](int i) {
     return descending ? (p.nchunks - 1 - (chunk0 + i)) : (chunk0 + i);
@@ -255,8 +267,7 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
     constexpr uint32_t IDESC_KV_SUB = IDESC_KV_ADD | (1u << 13);               // S -= K^T V (A negated)
     const uint32_t IDESC_KV = tms ? IDESC_KV_SUB : IDESC_KV_ADD;
     const uint32_t tP = tmem_base + cfg::P_COL;
-    const uint32_t tPb = tmem_base + cfg::PB_COL;
-    const uint32_t tO = tmem_base + cfg::O_COL;
+    const uint32_t tO0 = tmem_base + cfg::O_COL;
     const uint32_t tS = tmem_base + cfg::S_COL;
     const bool leader = ptx::elect_one();
     auto wait_tile = [&](int t) { return wait_uniform(full_bar(t % NSLOT), (t / NSLOT) & 1); };
@@ -266,7 +277,6 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
     // P = Q K^T of chunk i (both operands K-major, 16 columns of dk per instruction)
     auto issue_qk = [&](int i) {
       if (!wait_tile(3 * i)) return false;  // covers the k tile too
-      ptx::tc_fence_after();
       const uint32_t q_lo = ptx::desc_lo(slot_addr(3 * i), 16);
       const uint32_t k_lo = ptx::desc_lo(slot_addr(3 * i + 1), 16);
       if (leader) {
@@ -281,7 +291,7 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       return true;
     };
     if (mode == 0) {
-      uint32_t qs_waits = 0;
+      uint32_t sb_waits = 0;
       bool ok = issue_qk(0);
       for (int i = 0; ok && i < n_iter; ++i) {
         // descriptor low words: q K-major; k, v and the state buffer MN-major (64-column groups
@@ -294,14 +304,17 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         const bool use_state = have_state && !plain_chunk(i);
         const uint32_t acc0 = have_state ? 1u : 0u;   // S accumulates
         const uint32_t acc_o = use_state ? 1u : 0u;   // O already holds Q Sb
+        const uint32_t tO = tO0 + (i & 1) * DV;  // O accumulators alternate between two buffers
         FLA_TRACE_EVENT(0, i);
+        // The buffer was last used by chunk i-2; the epilogue must have drained it.
+        if (i >= 2 && !wait_uniform(o_free0 + 8u * (i & 1), ((i >> 1) - 1) & 1)) break;
+        FLA_TRACE_EVENT(26, i);
         // ---- O = Q Sb  (inter-chunk part; Sb is dk x dv, dv contiguous: MN-major B). Needs the
-        // converted state of the previous chunk and the O accumulator drained by the epilogue.
+        // converted state of the previous chunk.
         if (have_state) {
-          if (!wait_uniform(qs_ready, qs_waits & 1)) break;
-          ++qs_waits;
+          if (!wait_uniform(sb_ready, sb_waits & 1)) break;
+          ++sb_waits;
           FLA_TRACE_EVENT(2, i);
-          ptx::tc_fence_after();
           if (leader && use_state) {
 #pragma unroll
             for (int kk = 0; kk < DK / 16; ++kk) {
@@ -318,7 +331,6 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         // the K tile in shared memory and land in TMEM lanes nobody reads.
         if (!wait_tile(3 * i + 2)) break;
         FLA_TRACE_EVENT(4, i);
-        ptx::tc_fence_after();
         if (leader) {
 #pragma unroll
           for (int kk = 0; kk < kChunk / 16; ++kk) {
@@ -330,16 +342,29 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         release_tile(3 * i + 1);
         FLA_TRACE_EVENT(5, i);
         // ---- O += Pb V  (A from TMEM: 16 bf16 = 8 columns per instruction; V MN-major)
+#ifdef FLA_TRACE
+        {
+          FLA_TRACE_EVENT(17, i);
+          const int okw = ptx::mbar_wait(pb_ready, i & 1, abort_flag) ? 1 : 0;
+          FLA_TRACE_EVENT(18, i);
+          if (!__all_sync(0xffffffffu, okw)) break;
+          FLA_TRACE_EVENT(19, i);
+        }
+#else
         if (!wait_uniform(pb_ready, i & 1)) break;
+#endif
         FLA_TRACE_EVENT(6, i);
         ptx::tc_fence_after();
+        FLA_TRACE_EVENT(9, i);
         if (leader) {
 #pragma unroll
           for (int kk = 0; kk < kChunk / 16; ++kk) {
-            ptx::mma_ts(tO, tPb + kk * 8, v_lo + kk * (2048 >> 4), ptx::kDescHi, IDESC_PV,
+            // bf16 P of tokens 16kk..16kk+15: 8 columns, in place over the fp32 tile
+            const uint32_t pb = tP + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
+            ptx::mma_ts(tO, pb, v_lo + kk * (2048 >> 4), ptx::kDescHi, IDESC_PV,
                         kk > 0 ? 1u : acc_o);
           }
-          ptx::tc_commit(o_full);
+          ptx::tc_commit((i & 1) ? o_full1 : o_full0);
         }
         release_tile(3 * i + 2);
         FLA_TRACE_EVENT(7, i);
@@ -432,7 +457,7 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       ptx::tc_wait_st();
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before();
-      ptx::mbar_arrive(qs_ready);
+      ptx::mbar_arrive(sb_ready);
     }
 
     if (mode == 0) {
@@ -446,40 +471,53 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         ptx::tc_fence_after();
         // Column blocks of 32: relative to this warp's 32 rows a block is entirely kept, entirely
         // masked, or (block index == quadrant) the diagonal block that needs per-element tests.
-        uint32_t pk[16];
-        const bool tms_i = tms && !plain_chunk(i);     // subtract the strictly upper part
-        const bool upper = tms_i || upper_flag;         // which side of the diagonal is kept
+        // The three mask modes are compiled separately (MODE 0: keep col <= row; 1: keep
+        // col >= row; 2: keep col > row and negate) and selected by a warp-uniform branch.
+        auto p_convert = [&](auto mode_c) {
+          constexpr int MODE = decltype(mode_c)::value;
+          constexpr bool kUpper = MODE != 0;
+          uint32_t pk[16];
 #pragma unroll
-        for (int jb = 0; jb < 2; ++jb) {
-          const int cb = half * 2 + jb;
-          const bool masked = upper ? (cb < quad) : (cb > quad);  // warp-uniform
-          if (masked) {
+          for (int jb = 0; jb < 2; ++jb) {
+            const int cb = half * 2 + jb;
+            const bool masked = kUpper ? (cb < quad) : (cb > quad);  // warp-uniform
+            if (masked) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) pk[j] = 0u;
-          } else {
-            ptx::tmem_ld32(lane_base + cfg::P_COL + cb * 32, ra);
-            ptx::tc_wait_ld();
-            if (cb == quad) {
-              // first kept column (upper) resp. last kept column (lower) of this thread's row
-              const int edge = tms_i ? lane + 1 : lane;
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const bool k0 = upper ? (2 * j >= edge) : (2 * j <= edge);
-                const bool k1 = upper ? (2 * j + 1 >= edge) : (2 * j + 1 <= edge);
-                pk[j] = ptx::pack_bf16x2(k0 ? __uint_as_float(ra[2 * j]) : 0.f,
-                                         k1 ? __uint_as_float(ra[2 * j + 1]) : 0.f);
-              }
+              for (int j = 0; j < 16; ++j) pk[j] = 0u;
             } else {
+              ptx::tmem_ld32(lane_base + cfg::P_COL + cb * 32, ra);
+              ptx::tc_wait_ld();
+              if (cb == quad) {
+                // first kept column (upper modes) resp. last kept column (lower) of this row
+                const int edge = (MODE == 2) ? lane + 1 : lane;
 #pragma unroll
-              for (int j = 0; j < 16; ++j)
-                pk[j] = ptx::pack_bf16x2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1]));
-            }
-            if (tms_i) {
+                for (int j = 0; j < 16; ++j) {
+                  const bool k0 = kUpper ? (2 * j >= edge) : (2 * j <= edge);
+                  const bool k1 = kUpper ? (2 * j + 1 >= edge) : (2 * j + 1 <= edge);
+                  pk[j] = ptx::pack_bf16x2(k0 ? __uint_as_float(ra[2 * j]) : 0.f,
+                                           k1 ? __uint_as_float(ra[2 * j + 1]) : 0.f);
+                }
+              } else {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) pk[j] ^= 0x80008000u;  // negate both halves
+                for (int j = 0; j < 16; ++j)
+                  pk[j] =
+                      ptx::pack_bf16x2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1]));
+              }
+              if (MODE == 2) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) pk[j] ^= 0x80008000u;  // negate both halves
+              }
             }
+            // in place: this group's 64 fp32 columns shrink to 32 columns at the start of them
+            ptx::tmem_st16(lane_base + cfg::P_COL + half * 64 + jb * 16, pk);
           }
-          ptx::tmem_st16(lane_base + cfg::PB_COL + cb * 16, pk);
+        };
+        if (tms && !plain_chunk(i)) {
+          p_convert(std::integral_constant<int, 2>{});
+        } else if (upper_flag) {
+          p_convert(std::integral_constant<int, 1>{});
+        } else {
+          p_convert(std::integral_constant<int, 0>{});
         }
         if (warp == 2) FLA_TRACE_EVENT(12, i);
         ptx::tc_wait_st();
@@ -501,7 +539,7 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
           if (!last) {
             ptx::fence_proxy_async_smem();
             ptx::tc_fence_before();
-            ptx::mbar_arrive(qs_ready);
+            ptx::mbar_arrive(sb_ready);
           }
           if (warp == 2) FLA_TRACE_EVENT(16, i);
         }
@@ -522,23 +560,20 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       const int row = quad * 32 + lane;
       const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
       const uint32_t swz = static_cast<uint32_t>(row & 7);
-      const bool leader = (threadIdx.x == 10 * 32);
       uint32_t ra[32], rb[32];
       uint32_t pk[DV / 2];
-      // With an initial state the first "state ready" phase has no drained accumulator to wait
-      // for; the epilogue's share of that phase is given here.
-      if (has_init) ptx::mbar_arrive(qs_ready);
       for (int i = 0; i < n_iter; ++i) {
         if (warp == 10) FLA_TRACE_EVENT(20, i);
-        int ok = ptx::mbar_wait(o_full, i & 1, abort_flag) ? 1 : 0;
+        // one barrier per accumulator buffer: the MMA warp may run a chunk ahead of this group
+        int ok = ptx::mbar_wait((i & 1) ? o_full1 : o_full0, (i >> 1) & 1, abort_flag) ? 1 : 0;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         if (warp == 10) FLA_TRACE_EVENT(21, i);
         ptx::tc_fence_after();
 #pragma unroll
         for (int cb = 0; cb < DV / 32; cb += 2) {
-          ptx::tmem_ld32(lane_base + cfg::O_COL + cb * 32, ra);
-          ptx::tmem_ld32(lane_base + cfg::O_COL + (cb + 1) * 32, rb);
+          ptx::tmem_ld32(lane_base + cfg::O_COL + (i & 1) * DV + cb * 32, ra);
+          ptx::tmem_ld32(lane_base + cfg::O_COL + (i & 1) * DV + (cb + 1) * 32, rb);
           ptx::tc_wait_ld();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -549,14 +584,13 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
           }
         }
         ptx::tc_fence_before();
-        ptx::mbar_arrive(qs_ready);
+        ptx::mbar_arrive(o_free0 + 8u * (i & 1));
         if (warp == 10) FLA_TRACE_EVENT(22, i);
-        // The staging buffer is free once the previous chunk's TMA store has read it.
-        if (i > 0) {
-          ok = ptx::mbar_wait(ost_free, (i - 1) & 1, abort_flag) ? 1 : 0;
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-        }
+        // Every warp stages and stores its own 32 rows (a 64 x 32 box per column group), so no
+        // barrier spans the group and nobody waits for a store except the warp that issued it:
+        // before overwriting its rows, lane 0 checks that the previous store has read them.
+        if (lane == 0) ptx::bulk_wait_group_read0();
+        __syncwarp();
         const uint32_t obuf = ost_addr + row * 128;
 #pragma unroll
         for (int gg = 0; gg < cfg::GV; ++gg) {
@@ -568,22 +602,20 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
           }
         }
         ptx::fence_proxy_async_smem();
-        ptx::mbar_arrive(o_staged);
+        __syncwarp();
         if (warp == 10) FLA_TRACE_EVENT(23, i);
-        // One thread waits (bounded) until all 128 rows are staged, then issues the store.
-        if (leader && ptx::mbar_wait(o_staged, i & 1, abort_flag)) {
-          const int tok = mem_chunk(i) * kChunk;
+        const int tok = mem_chunk(i) * kChunk + quad * 32;
+        if (lane == 0 && tok < pr.n_tokens) {
 #pragma unroll
           for (int gg = 0; gg < cfg::GV; ++gg)
-            ptx::tma_store_4d(&pr.o, ost_addr + gg * kGroupBytes, gg * 64, tok, h, b);
+            ptx::tma_store_4d(&pr.o, ost_addr + gg * kGroupBytes + quad * (32 * 128), gg * 64, tok,
+                              h, b);
           ptx::bulk_commit_group();
           FLA_TRACE_EVENT(24, i);
-          ptx::bulk_wait_group_read0();
-          ptx::mbar_arrive(ost_free);
-          FLA_TRACE_EVENT(25, i);
         }
       }
-      if (leader) ptx::bulk_wait_group0();
+      if (lane == 0) ptx::bulk_wait_group0();
+
     }
   }
 
