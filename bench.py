@@ -33,6 +33,7 @@ WORKLOADS = {
     "cfg2": (8, 16, 4096, 64, 64),
     "cfg3": (4, 32, 8192, 128, 128),
     "cfg3_small": (4, 32, 1024, 128, 128),  # cfg3's head count at N=1024: sized for ncu captures
+    "cfg3_half": (4, 32, 4096, 128, 128),   # cfg3 at half the sequence length (1 GB resident)
     "cfg5": (1, 32, 65536, 128, 128),
 }
 METRIC = "fwd+bwd Mtokens/s, N=8K D=128 bf16, 1/2/4/8 B200; % tensor/HBM roofline"

@@ -8,18 +8,19 @@
 // product with the operands permuted (see fla_api.cu), which replaces the quadratic tile loops of
 // flashlinear/kernels/linear_attn_kernels.py:63-85 (fwd), :171-200 and :283-302 (bwd).
 //
-// CTA layout (448 threads, one CTA per SM):
+// CTA layout (480 threads, one CTA per SM):
 //   warp 0        TMA producer: Q, K, V chunk tiles -> a ring of shared-memory slots (128B swizzle)
-//   warp 1        tcgen05.mma issuer (one thread) and TMEM owner
+//   warp 1        MMA issuer X (one elected lane) and TMEM owner: S += K^T V, P = Q K^T
+//   warp 14       MMA issuer Y (one elected lane): O = Q Sb, O += Pb V
 //   warps 2-5     converter group A  } P fp32 (TMEM) -> mask -> bf16 (TMEM, A operand of P V)
 //   warps 6-9     converter group B  } S fp32 (TMEM) -> bf16 (shared memory, B operand of Q S);
 //                                      each group owns one half of the columns
 //   warps 10-13   epilogue group: O fp32 (TMEM) -> bf16 -> staging buffer -> TMA store
 //
-// MMA issue order per chunk i (steady state):  O = Q_i Sb_{i-1};  S += K_i^T V_i;  O += Pb_i V_i;
-// P = Q_{i+1} K_{i+1}^T.  The score tile of the NEXT chunk is issued last so that its conversion
-// overlaps the first two MMAs of that chunk, and the state conversion overlaps the last two of
-// this one; the only loop-carried dependency is the state.
+// Two warps issue MMAs so that the waits of one overlap the issue of the other: X produces the
+// intermediates (state S, score tile P of the NEXT chunk), Y consumes their bf16 forms into the
+// output accumulator. Orderings that a single issuing thread would get for free are explicit
+// mbarrier edges here (see the role comments).
 #pragma once
 #include "ptx.cuh"
 
@@ -28,7 +29,7 @@
 namespace fla {
 
 constexpr int kChunk = 128;                // tokens per chunk (= MMA M)
-constexpr int kThreads = 448;              // 14 warps
+constexpr int kThreads = 480;              // 15 warps
 constexpr int kGroupBytes = kChunk * 128;  // one 64-column group of a chunk tile: 128 rows x 128 B
 
 struct Problem {
@@ -103,10 +104,10 @@ struct Cfg {
   static_assert(SMEM_BYTES <= SMEM_LIMIT, "shared memory budget");
   static_assert((2 * NSLOT + 10) * 8 + 16 <= BAR_BYTES, "barrier area");
   // TMEM columns (32-bit each, 128 lanes)
-  static constexpr int P_COL = 0;   // P fp32: 128 columns. Its bf16 form (two per column) is written
-                                    // in place: columns [0,32) for tokens 0-63, [64,96) for 64-127.
-  static constexpr int O_COL = 128;           // O fp32: two buffers of DV columns (even / odd chunk)
-  static constexpr int S_COL = 128 + 2 * DV;  // S fp32: DV columns, lane = dk index
+  static constexpr int P_COL = 0;         // P fp32: 128 columns
+  static constexpr int PB_COL = 128;      // P bf16 (two per column): two buffers of 64 columns
+  static constexpr int O_COL = 256;       // O fp32: DV columns
+  static constexpr int S_COL = 256 + DV;  // S fp32: DV columns, lane = dk index
   static constexpr int TMEM_COLS = 512;
   static_assert(S_COL + DV <= TMEM_COLS, "TMEM budget");
 };
@@ -139,10 +140,14 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
   auto empty_bar = [&](int s) { return bar_base + 8u * (NSLOT + s); };
   const uint32_t p_full = bar_base + 8u * (2 * NSLOT + 0);
   const uint32_t pb_ready = bar_base + 8u * (2 * NSLOT + 1);
-  const uint32_t o_full0 = bar_base + 8u * (2 * NSLOT + 2);  // buffer 1: o_full1
-  const uint32_t o_full1 = bar_base + 8u * (2 * NSLOT + 9);
+  // One o_full barrier per bf16-P buffer (chunk parity): a waiter that needs "chunk i-1 is done"
+  // must not be overtaken by the completion for chunk i, which a shared barrier would allow.
+  const uint32_t o_full0 = bar_base + 8u * (2 * NSLOT + 2);
+  const uint32_t o_full1 = bar_base + 8u * (2 * NSLOT + 7);
+  const uint32_t qs_done = bar_base + 8u * (2 * NSLOT + 6);
+  const uint32_t p_read = bar_base + 8u * (2 * NSLOT + 8);
   const uint32_t sb_ready = bar_base + 8u * (2 * NSLOT + 3);
-  const uint32_t o_free0 = bar_base + 8u * (2 * NSLOT + 5);  // o_free0 + 8: buffer 1
+  const uint32_t o_free = bar_base + 8u * (2 * NSLOT + 5);
   const uint32_t s_full = bar_base + 8u * (2 * NSLOT + 4);
   const uint32_t holder_off =
       NSLOT * cfg::TILE_BYTES + cfg::SB_BYTES + cfg::OST_BYTES + 8u * (2 * NSLOT + 10);
@@ -175,15 +180,17 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
     *abort_flag = 0;
     for (int s = 0; s < NSLOT; ++s) {
       ptx::mbar_init(full_bar(s), 1);
-      ptx::mbar_init(empty_bar(s), 1);
+      // mode 0: every tile is read by two MMA groups, each followed by a tcgen05.commit arrival
+      ptx::mbar_init(empty_bar(s), mode == 0 ? 2 : 1);
     }
     ptx::mbar_init(p_full, 1);
     ptx::mbar_init(pb_ready, 256);
     ptx::mbar_init(o_full0, 1);
     ptx::mbar_init(o_full1, 1);
+    ptx::mbar_init(qs_done, 1);
+    ptx::mbar_init(p_read, 256);
     ptx::mbar_init(sb_ready, 256);
-    ptx::mbar_init(o_free0, 128);
-    ptx::mbar_init(o_free0 + 8, 128);
+    ptx::mbar_init(o_free, 128);
     ptx::mbar_init(s_full, 1);
     ptx::fence_barrier_init();
     ptx::fence_proxy_async_smem();
@@ -257,17 +264,19 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       __syncwarp();
     }
   } else if (warp == 1) {
-    // ================================================================ MMA issuer
-    // The whole warp runs the loop with warp-uniform operands; one elected lane issues the
-    // tcgen05.mma / tcgen05.commit instructions.
+    // ================================================================ MMA issuer X
+    // S += K_i^T V_i, then P = Q_{i+1} K_{i+1}^T. The whole warp runs the loop with warp-uniform
+    // operands; one elected lane issues the tcgen05.mma / tcgen05.commit instructions.
+    // Edges it waits on besides tile arrival:
+    //   sb_ready(i-1)  the converters have read S of chunk i-1 out of TMEM      (before S += ..)
+    //   p_read(i)      the converters have read P of chunk i out of TMEM        (before P = ..)
+    //   o_full(i-1)    issuer Y's P V of chunk i-1 is done: that bf16 P buffer is reused by
+    //                  the conversion of the tile written here
     constexpr uint32_t IDESC_QK = ptx::make_idesc(128, kChunk, false, false);  // P  = Q K^T
-    constexpr uint32_t IDESC_PV = ptx::make_idesc(128, DV, false, true);       // O += Pb V
-    constexpr uint32_t IDESC_QS = ptx::make_idesc(128, DV, false, true);       // O  = Q Sb
     constexpr uint32_t IDESC_KV_ADD = ptx::make_idesc(128, DV, true, true);    // S += K^T V
     constexpr uint32_t IDESC_KV_SUB = IDESC_KV_ADD | (1u << 13);               // S -= K^T V (A negated)
     const uint32_t IDESC_KV = tms ? IDESC_KV_SUB : IDESC_KV_ADD;
     const uint32_t tP = tmem_base + cfg::P_COL;
-    const uint32_t tO0 = tmem_base + cfg::O_COL;
     const uint32_t tS = tmem_base + cfg::S_COL;
     const bool leader = ptx::elect_one();
     auto wait_tile = [&](int t) { return wait_uniform(full_bar(t % NSLOT), (t / NSLOT) & 1); };
@@ -287,6 +296,8 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         }
         ptx::tc_commit(p_full);
       }
+      release_tile(3 * i);      // first of two arrivals on q (the other: issuer Y after Q Sb)
+      release_tile(3 * i + 1);  // first of two arrivals on k (the other: below, after K^T V)
       __syncwarp();
       return true;
     };
@@ -294,88 +305,46 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       uint32_t sb_waits = 0;
       bool ok = issue_qk(0);
       for (int i = 0; ok && i < n_iter; ++i) {
-        // descriptor low words: q K-major; k, v and the state buffer MN-major (64-column groups
-        // kGroupBytes resp. DK*128 bytes apart)
-        const uint32_t q_lo = ptx::desc_lo(slot_addr(3 * i), 16);
+        // k, v MN-major: 64-column groups kGroupBytes apart
         const uint32_t k_lo = ptx::desc_lo(slot_addr(3 * i + 1), kGroupBytes);
         const uint32_t v_lo = ptx::desc_lo(slot_addr(3 * i + 2), kGroupBytes);
-        const uint32_t sb_lo = ptx::desc_lo(sb_addr, DK * 128);
         const bool have_state = (i > 0) || has_init;
-        const bool use_state = have_state && !plain_chunk(i);
-        const uint32_t acc0 = have_state ? 1u : 0u;   // S accumulates
-        const uint32_t acc_o = use_state ? 1u : 0u;   // O already holds Q Sb
-        const uint32_t tO = tO0 + (i & 1) * DV;  // O accumulators alternate between two buffers
         FLA_TRACE_EVENT(0, i);
-        // The buffer was last used by chunk i-2; the epilogue must have drained it.
-        if (i >= 2 && !wait_uniform(o_free0 + 8u * (i & 1), ((i >> 1) - 1) & 1)) break;
-        FLA_TRACE_EVENT(26, i);
-        // ---- O = Q Sb  (inter-chunk part; Sb is dk x dv, dv contiguous: MN-major B). Needs the
-        // converted state of the previous chunk.
-        if (have_state) {
-          if (!wait_uniform(sb_ready, sb_waits & 1)) break;
-          ++sb_waits;
-          FLA_TRACE_EVENT(2, i);
-          if (leader && use_state) {
-#pragma unroll
-            for (int kk = 0; kk < DK / 16; ++kk) {
-              const uint32_t off = ((kk >> 2) * kGroupBytes + (kk & 3) * 32) >> 4;
-              ptx::mma_ss(tO, q_lo + off, sb_lo + kk * (2048 >> 4), ptx::kDescHi, IDESC_QS,
-                          kk > 0 ? 1u : 0u);
-            }
-          }
-        }
-        release_tile(3 * i);  // q: read by the score MMA (issued earlier) and the one above
-        FLA_TRACE_EVENT(3, i);
         // ---- S += K^T V  (both operands MN-major: the token index is the MMA K dimension).
         // For DK = 64 the instruction still spans 128 rows; the upper 64 read whatever follows
         // the K tile in shared memory and land in TMEM lanes nobody reads.
+        if (have_state) {
+          if (!wait_uniform(sb_ready, sb_waits & 1)) break;
+          ++sb_waits;
+        }
+        FLA_TRACE_EVENT(2, i);
         if (!wait_tile(3 * i + 2)) break;
         FLA_TRACE_EVENT(4, i);
+        ptx::tc_fence_after();
         if (leader) {
 #pragma unroll
           for (int kk = 0; kk < kChunk / 16; ++kk) {
             ptx::mma_ss(tS, k_lo + kk * (2048 >> 4), v_lo + kk * (2048 >> 4), ptx::kDescHi,
-                        IDESC_KV, kk > 0 ? 1u : acc0);
+                        IDESC_KV, kk > 0 ? 1u : (have_state ? 1u : 0u));
           }
           ptx::tc_commit(s_full);
         }
         release_tile(3 * i + 1);
+        release_tile(3 * i + 2);  // first of two arrivals on v (the other: issuer Y after P V)
         FLA_TRACE_EVENT(5, i);
-        // ---- O += Pb V  (A from TMEM: 16 bf16 = 8 columns per instruction; V MN-major)
-#ifdef FLA_TRACE
-        {
-          FLA_TRACE_EVENT(17, i);
-          const int okw = ptx::mbar_wait(pb_ready, i & 1, abort_flag) ? 1 : 0;
-          FLA_TRACE_EVENT(18, i);
-          if (!__all_sync(0xffffffffu, okw)) break;
-          FLA_TRACE_EVENT(19, i);
+        // ---- score tile of the next chunk
+        if (i + 1 < n_iter) {
+          if (!wait_uniform(p_read, i & 1)) break;
+          if (i >= 1 && !wait_uniform(((i - 1) & 1) ? o_full1 : o_full0, ((i - 1) >> 1) & 1)) break;
+          FLA_TRACE_EVENT(6, i);
+          ptx::tc_fence_after();
+          ok = issue_qk(i + 1);
         }
-#else
-        if (!wait_uniform(pb_ready, i & 1)) break;
-#endif
-        FLA_TRACE_EVENT(6, i);
-        ptx::tc_fence_after();
-        FLA_TRACE_EVENT(9, i);
-        if (leader) {
-#pragma unroll
-          for (int kk = 0; kk < kChunk / 16; ++kk) {
-            // bf16 P of tokens 16kk..16kk+15: 8 columns, in place over the fp32 tile
-            const uint32_t pb = tP + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
-            ptx::mma_ts(tO, pb, v_lo + kk * (2048 >> 4), ptx::kDescHi, IDESC_PV,
-                        kk > 0 ? 1u : acc_o);
-          }
-          ptx::tc_commit((i & 1) ? o_full1 : o_full0);
-        }
-        release_tile(3 * i + 2);
-        FLA_TRACE_EVENT(7, i);
-        // ---- score tile of the next chunk (P fp32 is free: its conversion was awaited above)
-        if (i + 1 < n_iter) ok = issue_qk(i + 1);
         FLA_TRACE_EVENT(8, i);
       }
     } else {
       for (int i = 0; i < n_iter; ++i) {
         if (!wait_tile(2 * i) || !wait_tile(2 * i + 1)) break;
-        ptx::tc_fence_after();
         const uint32_t k_lo = ptx::desc_lo(slot_addr(2 * i), kGroupBytes);
         const uint32_t v_lo = ptx::desc_lo(slot_addr(2 * i + 1), kGroupBytes);
         if (leader) {
@@ -389,6 +358,66 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         release_tile(2 * i + 1);
         if (leader && i == n_iter - 1) ptx::tc_commit(s_full);
         __syncwarp();
+      }
+    }
+  } else if (warp == 14) {
+    // ================================================================ MMA issuer Y
+    // O = Q_i Sb_{i-1}, then O += Pb_i V_i. Edges besides tile arrival:
+    //   o_free(i-1)   the epilogue has drained the accumulator of chunk i-1
+    //   sb_ready(i-1) the bf16 state of chunk i-1 is in shared memory
+    //   pb_ready(i)   the bf16 score tile of chunk i is in TMEM
+    // and it signals qs_done(i) (the state buffer may be overwritten) and o_full(i).
+    if (mode == 0) {
+      constexpr uint32_t IDESC_PV = ptx::make_idesc(128, DV, false, true);  // O += Pb V
+      constexpr uint32_t IDESC_QS = ptx::make_idesc(128, DV, false, true);  // O  = Q Sb
+      const uint32_t tO = tmem_base + cfg::O_COL;
+      const uint32_t sb_lo = ptx::desc_lo(sb_addr, DK * 128);  // MN-major, groups DK*128 B apart
+      const bool leader = ptx::elect_one();
+      auto wait_tile = [&](int t) { return wait_uniform(full_bar(t % NSLOT), (t / NSLOT) & 1); };
+      uint32_t sb_waits = 0;
+      for (int i = 0; i < n_iter; ++i) {
+        const uint32_t q_lo = ptx::desc_lo(slot_addr(3 * i), 16);                // K-major
+        const uint32_t v_lo = ptx::desc_lo(slot_addr(3 * i + 2), kGroupBytes);  // MN-major
+        const bool have_state = (i > 0) || has_init;
+        const bool use_state = have_state && !plain_chunk(i);
+        const uint32_t tPb = tmem_base + cfg::PB_COL + (i & 1) * 64;
+        FLA_TRACE_EVENT(9, i);
+        if (i >= 1 && !wait_uniform(o_free, (i - 1) & 1)) break;
+        if (have_state) {
+          if (!wait_uniform(sb_ready, sb_waits & 1)) break;
+          ++sb_waits;
+        }
+        if (!wait_tile(3 * i)) break;
+        FLA_TRACE_EVENT(17, i);
+        ptx::tc_fence_after();
+        if (leader) {
+          if (use_state) {
+#pragma unroll
+            for (int kk = 0; kk < DK / 16; ++kk) {
+              const uint32_t off = ((kk >> 2) * kGroupBytes + (kk & 3) * 32) >> 4;
+              ptx::mma_ss(tO, q_lo + off, sb_lo + kk * (2048 >> 4), ptx::kDescHi, IDESC_QS,
+                          kk > 0 ? 1u : 0u);
+            }
+          }
+          ptx::tc_commit(qs_done);
+          ptx::tc_commit(empty_bar((3 * i) % NSLOT));  // second arrival on q
+        }
+        FLA_TRACE_EVENT(18, i);
+        if (!wait_uniform(pb_ready, i & 1)) break;
+        if (!wait_tile(3 * i + 2)) break;
+        FLA_TRACE_EVENT(19, i);
+        ptx::tc_fence_after();
+        if (leader) {
+#pragma unroll
+          for (int kk = 0; kk < kChunk / 16; ++kk) {
+            ptx::mma_ts(tO, tPb + kk * 8, v_lo + kk * (2048 >> 4), ptx::kDescHi, IDESC_PV,
+                        kk > 0 ? 1u : (use_state ? 1u : 0u));
+          }
+          ptx::tc_commit((i & 1) ? o_full1 : o_full0);
+          ptx::tc_commit(empty_bar((3 * i + 2) % NSLOT));  // second arrival on v
+        }
+        __syncwarp();
+        FLA_TRACE_EVENT(7, i);
       }
     }
   } else if (warp < 10) {
@@ -484,9 +513,17 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
             if (masked) {
 #pragma unroll
               for (int j = 0; j < 16; ++j) pk[j] = 0u;
+              if (jb == 1) {
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(p_read);
+              }
             } else {
               ptx::tmem_ld32(lane_base + cfg::P_COL + cb * 32, ra);
               ptx::tc_wait_ld();
+              if (jb == 1) {  // both blocks are in registers: issuer X may overwrite the fp32 tile
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(p_read);
+              }
               if (cb == quad) {
                 // first kept column (upper modes) resp. last kept column (lower) of this row
                 const int edge = (MODE == 2) ? lane + 1 : lane;
@@ -508,8 +545,7 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
                 for (int j = 0; j < 16; ++j) pk[j] ^= 0x80008000u;  // negate both halves
               }
             }
-            // in place: this group's 64 fp32 columns shrink to 32 columns at the start of them
-            ptx::tmem_st16(lane_base + cfg::P_COL + half * 64 + jb * 16, pk);
+            ptx::tmem_st16(lane_base + cfg::PB_COL + (i & 1) * 64 + cb * 16, pk);
           }
         };
         if (tms && !plain_chunk(i)) {
@@ -530,6 +566,8 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         const bool to_final = last && (pr.s_final != nullptr) && (g == nseg - 1);
         if (!last || to_final) {
           ok = ptx::mbar_wait(s_full, i & 1, abort_flag) ? 1 : 0;
+          // the state buffer is still the B operand of issuer Y's Q Sb of this chunk
+          if (ok && !last) ok = ptx::mbar_wait(qs_done, i & 1, abort_flag) ? 1 : 0;
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           if (warp == 2) FLA_TRACE_EVENT(14, i);
@@ -564,7 +602,6 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       uint32_t pk[DV / 2];
       for (int i = 0; i < n_iter; ++i) {
         if (warp == 10) FLA_TRACE_EVENT(20, i);
-        // one barrier per accumulator buffer: the MMA warp may run a chunk ahead of this group
         int ok = ptx::mbar_wait((i & 1) ? o_full1 : o_full0, (i >> 1) & 1, abort_flag) ? 1 : 0;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -572,8 +609,8 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         ptx::tc_fence_after();
 #pragma unroll
         for (int cb = 0; cb < DV / 32; cb += 2) {
-          ptx::tmem_ld32(lane_base + cfg::O_COL + (i & 1) * DV + cb * 32, ra);
-          ptx::tmem_ld32(lane_base + cfg::O_COL + (i & 1) * DV + (cb + 1) * 32, rb);
+          ptx::tmem_ld32(lane_base + cfg::O_COL + cb * 32, ra);
+          ptx::tmem_ld32(lane_base + cfg::O_COL + (cb + 1) * 32, rb);
           ptx::tc_wait_ld();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -584,7 +621,7 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
           }
         }
         ptx::tc_fence_before();
-        ptx::mbar_arrive(o_free0 + 8u * (i & 1));
+        ptx::mbar_arrive(o_free);
         if (warp == 10) FLA_TRACE_EVENT(22, i);
         // Every warp stages and stores its own 32 rows (a 64 x 32 box per column group), so no
         // barrier spans the group and nobody waits for a store except the warp that issued it:
