@@ -59,6 +59,7 @@ EXPORTED_SYMBOLS = (
     "fla_sm100_fwd",
     "fla_sm100_bwd",
     "fla_sm100_state",
+    "fla_sm100_fwd_static_scratch",
     "fla_sm100_last_launch_count",
 )
 
@@ -89,6 +90,8 @@ def load() -> ctypes.CDLL:
     lib.fla_sm100_bwd.argtypes = [ctypes.POINTER(FlaArgs)]
     lib.fla_sm100_state.restype = ctypes.c_int
     lib.fla_sm100_state.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_int]
+    lib.fla_sm100_fwd_static_scratch.restype = ctypes.c_int
+    lib.fla_sm100_fwd_static_scratch.argtypes = [ctypes.POINTER(FlaArgs)]
     lib.fla_sm100_last_launch_count.restype = ctypes.c_int
     if lib.fla_sm100_abi_version() != FLA_ABI_VERSION:
         raise ImportError("libflashlinear_sm100.so has a different ABI version; rebuild it")

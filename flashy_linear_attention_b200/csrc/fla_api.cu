@@ -374,6 +374,42 @@ int check_common(const FlaArgs* a, DeviceInfo** dev) {
   return FLA_OK;
 }
 
+// ---------------------------------------------------------------- scratch that nobody allocates
+// Scratch for fla_sm100_fwd_static_scratch(): a fixed array that is part of the loaded module, so
+// that a caller who is not in a position to allocate device memory can still run the segmented
+// forward. Every GPU that loads the library carries these bytes until the process exits.
+// NOTE for host code: the NAME of this array is only a host-side handle. Its device address is
+// obtained with cudaGetSymbolAddress() (static_scratch_address() below) and that pointer is what
+// the kernels receive.
+static __device__ __align__(256) unsigned char g_static_scratch[FLA_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the current device, looked up once per device.
+int static_scratch_address(void** out) {
+  static void* addr[64];
+  static std::atomic<int> ready[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
+  if (ready[dev].load(std::memory_order_acquire) != 2) {
+    int expected = 0;
+    if (ready[dev].compare_exchange_strong(expected, 1)) {
+      void* p = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);  // device `dev` is current
+      if (e != cudaSuccess || p == nullptr) {
+        ready[dev].store(0, std::memory_order_release);
+        return FLA_ERR_CUDA;
+      }
+      addr[dev] = p;
+      ready[dev].store(2, std::memory_order_release);
+    } else {
+      while (ready[dev].load(std::memory_order_acquire) == 1) {
+      }
+      if (ready[dev].load(std::memory_order_acquire) != 2) return FLA_ERR_CUDA;
+    }
+  }
+  *out = addr[dev];
+  return FLA_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -393,6 +429,8 @@ const char* fla_sm100_strerror(int code) {
     case FLA_ERR_CUDA: return "a CUDA call failed";
     case FLA_ERR_WORKSPACE: return "workspace missing or too small";
     case FLA_ERR_DEVICE: return "current device is not an sm_100 GPU";
+    case FLA_ERR_SCRATCH_LIMIT:
+      return "shape needs more scratch than the built-in array of fla_sm100_fwd_static_scratch holds";
     default: return "unknown error";
   }
 }
@@ -522,6 +560,40 @@ int fla_sm100_state(const FlaArgs* a, int which) {
                      a->dk, a->dv, a->segments, a->r_final, a->workspace, a->workspace_bytes,
                      a->status, stream, *dev);
   return FLA_ERR_INVALID;
+}
+
+int fla_sm100_fwd_static_scratch(const FlaArgs* a) {
+  DeviceInfo* dev = nullptr;
+  g_last_launches = 0;
+  int rc = check_common(a, &dev);
+  if (rc) return rc;
+  // How much scratch this shape needs with the segment count the call will use.
+  const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
+  int nseg = a->segments > 0 ? a->segments
+                             : auto_segments(1, a->batch * a->heads, nchunks, dev->sm_count);
+  if (nseg > nchunks) nseg = nchunks;
+  if (nseg > 1) {
+    const int seg_chunks = (nchunks + nseg - 1) / nseg;
+    nseg = (nchunks + seg_chunks - 1) / seg_chunks;
+  }
+  const size_t need = segment_ws_bytes(1, a->batch * a->heads, nseg, a->dk, a->dv);
+  if (need > static_cast<size_t>(FLA_STATIC_SCRATCH_BYTES)) return FLA_ERR_SCRATCH_LIMIT;
+  void* scratch = nullptr;
+  if ((rc = static_scratch_address(&scratch)) != FLA_OK) return rc;
+  Product p;
+  p.a = operand(a->q, a->dk);
+  p.b = operand(a->k, a->dk);
+  p.c = operand(a->v, a->dv);
+  p.out = operand(a->o, a->dv);
+  p.flags = 0;
+  p.ext_init = a->s_init;
+  p.ext_final = a->s_final;
+  p.ext_trans = 0;
+  // Nothing in the scratch has to start at zero: every per-segment sum that the scan reads is
+  // written by the state pass of this same call first.
+  return run_products(&p, 1, a->batch, a->heads, a->seqlen, a->dk, a->dv, nseg, scratch,
+                      FLA_STATIC_SCRATCH_BYTES, a->status, static_cast<cudaStream_t>(a->stream),
+                      *dev);
 }
 
 }  // extern "C"

@@ -39,8 +39,12 @@ enum {
   FLA_ERR_ALIGNMENT = -3,   /* pointer or byte stride not a multiple of 16 */
   FLA_ERR_CUDA = -4,        /* a CUDA runtime / driver call failed */
   FLA_ERR_WORKSPACE = -5,   /* workspace missing or too small */
-  FLA_ERR_DEVICE = -6       /* current device is not compute capability 10.x */
+  FLA_ERR_DEVICE = -6,      /* current device is not compute capability 10.x */
+  FLA_ERR_SCRATCH_LIMIT = -7 /* fla_sm100_fwd_static_scratch: shape exceeds the built-in scratch */
 };
+
+/* Size of the built-in scratch array used by fla_sm100_fwd_static_scratch(). */
+#define FLA_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
 
 /* One [batch, heads, seqlen, dim] bf16 tensor: device pointer and element strides of the three
  * outer dimensions (the innermost stride is 1). */
@@ -109,6 +113,27 @@ int fla_sm100_bwd(const FlaArgs* args);
  * calling fla_sm100_fwd / fla_sm100_bwd with s_init / r_init. The reference has no counterpart:
  * its kernels are quadratic and keep no state (flashlinear/kernels/linear_attn_kernels.py:63). */
 int fla_sm100_state(const FlaArgs* args, int which);
+
+/* Forward pass for callers that cannot obtain device memory themselves.
+ * It has no counterpart in the reference (whose wrappers allocate through torch).
+ *
+ * Some integrations must not call cudaMalloc or any allocating library routine at the point where
+ * the attention runs: for instance a plugin that executes inside another runtime's memory plan, a
+ * real-time serving loop that forbids allocation after start-up, or host code that only receives
+ * raw input / output pointers. The ordinary fla_sm100_fwd() needs caller-provided scratch as soon as
+ * the sequence is split into segments (few heads, long sequences). This variant takes the same
+ * FlaArgs (q, k, v, o, optional s_init / s_final, segments, status, stream; workspace fields are
+ * ignored) and keeps the per-segment states in a fixed array of FLA_STATIC_SCRATCH_BYTES that is
+ * part of the library image on every GPU that loads it.
+ *  - It performs no device allocation or free, directly or through a library.
+ *  - Shapes whose segment states (batch*heads*segments*dk*dv*4 bytes) exceed the array are refused
+ *    with FLA_ERR_SCRATCH_LIMIT before anything is launched; pass a smaller `segments`.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *    that device current). Make that first call outside any stream capture.
+ *  - All calls on a device share the one array. Calls whose kernels may overlap on the GPU (other
+ *    streams, other host threads) race on it; serialise them. Nothing in it needs clearing
+ *    between calls: each call writes every entry it later reads. */
+int fla_sm100_fwd_static_scratch(const FlaArgs* args);
 
 /* Number of kernels the last fwd / bwd call on this thread launched (for benchmarks). */
 int fla_sm100_last_launch_count(void);
