@@ -6,9 +6,10 @@ One "step" = one forward + one backward of `LinearAttention` over the whole work
 Headline workload (cfg3): bf16, B=4, H=32, N=8192, dk=dv=128; q, k = elu(N(0,1)) + 1,
 v, dO ~ N(0,1), seeded synthetic data. Metric: Mtokens/s = B*N / step time, whole job.
 
-At N > 1 (launched by torch.distributed.run, one rank per GPU) the batch*heads independent heads
-of the SAME workload are split over the ranks (strong scaling; no data-path collective), timing is
-barrier + max over ranks. Prints one JSON line on rank 0.
+At N > 1 (launched by torch.distributed.run, one rank per GPU) the heads are independent, so the
+job is sharded by batch*head with no data-path collective: by default every GPU runs the whole
+workload (weak scaling, global batch = B x N); `--scaling strong` splits the B*H heads of the one
+workload over the GPUs instead. Timing is barrier + max over ranks; one JSON line on rank 0.
 
 `--impl reference` times the reference's naive PyTorch path (restated in oracle/torch_naive.py) on
 the host cores, on a bounded sample of the same workload.
@@ -22,6 +23,7 @@ import statistics
 import subprocess
 import sys
 import threading
+import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -65,9 +67,11 @@ def algorithmic_bytes(B, H, N, dk, dv):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi. It is started before the warm-up
+    (nvidia-smi needs ~100 ms to deliver its first sample) and only the samples that fall inside
+    the timed region, by wall clock, are reported."""
 
-    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
@@ -80,7 +84,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "20", "-i", str(self.index)],
+                 "-lms", "10", "-i", str(self.index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -89,35 +93,49 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
-    def stop(self):
+    def stop(self, t_start: float, t_end: float):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
         self.thread.join(timeout=2)
-        sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                smax.append(float(parts[1]))
-            except ValueError:
-                continue
-            for nme, val in zip(names, parts[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(nme)
+
+        def parse(window):
+            sm, smax, reasons = [], [], set()
+            for stamp, line in self.lines:
+                if window and not (t_start <= stamp <= t_end + 0.02):
+                    continue
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 8:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    smax.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for nme, val in zip(names, parts[4:8]):
+                    if val.lower().startswith("active"):
+                        reasons.add(nme)
+            return sm, smax, reasons
+
+        sm, smax, reasons = parse(True)
+        scope = "timed region"
+        if not sm:  # region shorter than the sampling period: fall back to the whole run
+            sm, smax, reasons = parse(False)
+            scope = "whole run (timed region shorter than one sample)"
         return {
             "sm_mhz": statistics.median(sm) if sm else None,
+            "sm_min_mhz": min(sm) if sm else None,
             "sm_max_mhz": max(smax) if smax else None,
             "samples": len(sm),
+            "scope": scope,
             "reasons": sorted(reasons),
         }
 
@@ -131,27 +149,26 @@ def make_inputs(B, H, N, dk, dv, device, seed=0):
     return q, k, v, dy
 
 
-def cpu_baseline_sample(B, H, N, dk, dv, budget_s=15.0, max_heads=8):
-    """Times the naive PyTorch path (oracle port) on the host on a bounded sample: whole heads of
-    one batch entry at the full sequence length. Returns the cpu_baseline dict."""
+def cpu_baseline_sample(B, H, N, dk, dv, budget_s=12.0, heads=8):
+    """Times the naive PyTorch path (oracle port) on the host on a bounded sample: `heads` whole
+    heads of one batch entry at the full sequence length per pass, repeated for about `budget_s`
+    seconds of CPU work. Returns the cpu_baseline dict."""
     from oracle import torch_naive
 
     threads = os.cpu_count() or 1
-    t1, used = torch_naive.time_fwd_bwd_cpu(1, 1, N, dk, dv, steps=1, warmup=0, threads=threads)
-    heads = int(max(1, min(max_heads, budget_s // max(t1, 1e-3))))
-    if heads > 1:
-        t, used = torch_naive.time_fwd_bwd_cpu(1, heads, N, dk, dv, steps=1, warmup=0, threads=threads)
-    else:
-        t = t1
+    heads = min(heads, H)
+    t1, used = torch_naive.time_fwd_bwd_cpu(1, heads, N, dk, dv, steps=1, warmup=0, threads=threads)
+    reps = int(max(1, min(30, budget_s // max(t1, 1e-3))))
+    t, used = torch_naive.time_fwd_bwd_cpu(1, heads, N, dk, dv, steps=reps, warmup=0, threads=threads)
     tokens_equiv = N * heads / H  # a token counts once all H heads of it are done
     return {
         "value": tokens_equiv / t / 1e6,
         "unit": UNIT,
         "cores": used,
         "kind": "port",
-        "sample": f"{heads} of {B * H} heads at full N={N}, fp32 fwd+autograd bwd, {t:.2f} s; "
-                  f"scaled to tokens by heads/{H}",
-        "seconds": t,
+        "sample": f"{heads} of {B * H} heads at full N={N}, fp32 fwd+autograd bwd, mean of {reps} passes "
+                  f"of {t:.2f} s; scaled to tokens by heads/{H}",
+        "seconds": t * reps,
     }
 
 
@@ -162,12 +179,12 @@ def run_reference(args, rank, world):
     from oracle import torch_naive
 
     threads = os.cpu_count() or 1
-    heads = 1
+    heads = min(8, H)
     total = args.warmup + args.steps
     t_probe, used = torch_naive.time_fwd_bwd_cpu(1, heads, N, dk, dv, steps=1, threads=threads)
-    # keep the whole run within a few minutes
-    if t_probe * total > 150:
-        steps, warmup = max(1, int(150 // t_probe) - 1), 1
+    # keep the whole run near a minute of CPU work
+    if t_probe * total > 60:
+        steps, warmup = max(1, int(60 // t_probe) - 1), 1
     else:
         steps, warmup = args.steps, args.warmup
     t, used = torch_naive.time_fwd_bwd_cpu(1, heads, N, dk, dv, steps=steps, warmup=warmup, threads=threads)
@@ -177,7 +194,7 @@ def run_reference(args, rank, world):
         "impl": "reference",
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": t * 1e3,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"{args.workload}: B={B} H={H} N={N} dk={dk} dv={dv}",
                    "sample": sample},
@@ -196,6 +213,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="N>1: weak = every GPU runs the whole workload (global batch = B x N); "
+                         "strong = the workload's batch*heads are split over the GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
 
@@ -223,9 +243,11 @@ def main():
 
     B, H, N, dk, dv = WORKLOADS[args.workload]
     q, k, v, dy = make_inputs(B, H, N, dk, dv, device)
-    if world > 1:
+    strong = args.scaling == "strong" and world > 1
+    if strong:
         q, k, v, dy = (shard_batch_heads(t, rank, world).contiguous() for t in (q, k, v, dy))
     Bl, Hl = q.shape[0], q.shape[1]
+    global_batch = B if (strong or world == 1) else B * world
     torch.cuda.empty_cache()
     warmup = max(args.warmup, 3)
     steps = args.steps
@@ -244,6 +266,9 @@ def main():
     if ops.backward_uses_final_state(q, v):
         s_state = torch.empty(Bl * Hl, dk, dv, dtype=torch.float32, device=device)
     launches = 0
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(warmup):
         ops.causal_dot_product_fwd(q, k, v, s_final=s_state)
         launches_f = lib.fla_sm100_last_launch_count()
@@ -252,10 +277,8 @@ def main():
     barrier()
     ops.check_status(device)
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     barrier()
+    t_region0 = time.time()
     for i in range(steps):
         ev[i][0].record(stream)
         ops.causal_dot_product_fwd(q, k, v, s_final=s_state)
@@ -263,7 +286,7 @@ def main():
         ops.causal_dot_product_bwd(dy, q, k, v, s_last=s_state)
         ev[i][2].record(stream)
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_region0, time.time()) if rank == 0 else None
     ops.check_status(device)
     total_ms = ev[0][0].elapsed_time(ev[-1][2])
     fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / steps
@@ -274,7 +297,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms, fwd_ms, bwd_ms = (float(x) for x in t.tolist())
     ms_per_step = total_ms / steps
-    value = B * N / (ms_per_step * 1e-3) / 1e6
+    value = global_batch * N / (ms_per_step * 1e-3) / 1e6
 
     # ---------------------------------------------------------------- end to end, host buffers
     e2e_steps = max(1, min(args.e2e_steps, steps))
@@ -302,7 +325,7 @@ def main():
     e2e_ms = torch.tensor([e0.elapsed_time(e1) / e2e_steps], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
-    e2e_value = B * N / (float(e2e_ms.item()) * 1e-3) / 1e6
+    e2e_value = global_batch * N / (float(e2e_ms.item()) * 1e-3) / 1e6
     h2d_total = torch.tensor([h2d, d2h], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(h2d_total, op=dist.ReduceOp.SUM)
@@ -316,10 +339,12 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
             "config": {
-                "workload": f"{args.workload}: LinearAttention fwd+bwd B={B} H={H} N={N} dk={dk} dv={dv}, "
-                            f"q,k=elu(N(0,1))+1, v,dO~N(0,1), seed 0",
+                "workload": f"{args.workload}: LinearAttention fwd+bwd B={B} H={H} N={N} dk={dk} dv={dv} per "
+                            f"{'job' if strong or world == 1 else 'GPU'}, q,k=elu(N(0,1))+1, v,dO~N(0,1), seed 0",
+                "global_batch": global_batch, "seq_len": N,
                 "parallelism": f"batch*head sharded over {world} GPU(s): {Bl}x{Hl} heads per GPU, no collective",
                 "l2": f"per-GPU working set {8 * q.numel() * 2 / 1e6:.0f} MB exceeds the 126 MB L2; no flush between steps",
                 "chunk": 128,
