@@ -172,7 +172,7 @@ def cpu_baseline_sample(B, H, N, dk, dv, budget_s=12.0, heads=8):
     }
 
 
-def run_reference(args, rank, world):
+def run_reference(args, rank, world, emit):
     if rank != 0:
         return
     B, H, N, dk, dv = WORKLOADS[args.workload]
@@ -202,10 +202,18 @@ def run_reference(args, rank, world):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def main():
+    # Libraries (NCCL's version banner, for one) print to stdout; the contract is ONE JSON line
+    # there, so everything else is sent to stderr and the line goes to the saved descriptor.
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(line: dict) -> None:
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
+
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -224,7 +232,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
 
     if args.impl == "reference":
-        run_reference(args, rank, world)
+        run_reference(args, rank, world, emit)
         return
 
     if not torch.cuda.is_available():
@@ -366,7 +374,7 @@ def main():
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_sample(B, H, N, dk, dv)
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -120,7 +120,7 @@ struct ScanParams {
 };
 
 __global__ void fla_state_scan_kernel(const ScanParams sp) {
-  const ScanProblem& pr = sp.prob[blockIdx.z];
+  const ScanProblem pr = sp.prob[blockIdx.z];
   const int bh = blockIdx.y;
   const int elems = sp.rows * sp.cols;
   const int e = blockIdx.x * blockDim.x + threadIdx.x;
@@ -129,13 +129,24 @@ __global__ void fla_state_scan_kernel(const ScanParams sp) {
   const size_t ext_idx = static_cast<size_t>(bh) * elems +
                          (pr.ext_trans ? static_cast<size_t>(col) * sp.rows + row : e);
   float run = pr.ext_init ? pr.ext_init[ext_idx] : 0.f;
-  float* base = pr.ws + static_cast<size_t>(bh) * sp.nseg * elems + e;
-  for (int g = 0; g < sp.nseg; ++g) {
-    float* p = base + static_cast<size_t>(g) * elems;
-    const bool present = (g < sp.nseg - 1) || sp.have_last;
-    const float local = present ? *p : 0.f;
-    *p = run;
-    run += local;
+  float* __restrict__ base = pr.ws + static_cast<size_t>(bh) * sp.nseg * elems + e;
+  const int npresent = sp.have_last ? sp.nseg : sp.nseg - 1;  // segments whose sum was written
+  // Batches of 8 segments: all loads of a batch are issued before the dependent stores.
+  for (int g0 = 0; g0 < sp.nseg; g0 += 8) {
+    float local[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int g = g0 + j;
+      local[j] = (g < npresent) ? __ldcg(base + static_cast<size_t>(g) * elems) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int g = g0 + j;
+      if (g < sp.nseg) {
+        base[static_cast<size_t>(g) * elems] = run;
+        run += local[j];
+      }
+    }
   }
   if (pr.ext_final) pr.ext_final[ext_idx] = run;
 }
@@ -188,7 +199,9 @@ int pick_template(int da, int dc) {
 int auto_segments(int nprob, int bh, int nchunks, int sm_count) {
   const long ctas = static_cast<long>(nprob) * bh;
   if (ctas * 4 >= static_cast<long>(sm_count) * 3) return 1;  // already >= 75 % of the SMs
-  int want = static_cast<int>((2L * sm_count + ctas - 1) / ctas);
+  // One wave: as many segments as fit the SMs once (every CTA pays a fixed start-up cost, and the
+  // state pass re-reads b and c, so more, shorter segments do not pay).
+  int want = static_cast<int>(sm_count / ctas);
   int max_seg = nchunks / 2;  // at least two chunks per segment
   if (max_seg < 1) max_seg = 1;
   if (want > max_seg) want = max_seg;
