@@ -224,6 +224,9 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="N>1: weak = every GPU runs the whole workload (global batch = B x N); "
                          "strong = the workload's batch*heads are split over the GPUs")
+    ap.add_argument("--sharding", default=None, choices=["batch_head", "sequence"],
+                    help="N>1: batch_head (default) or sequence (default for cfg5): every GPU holds "
+                         "N/W tokens of every head and the per-GPU states are exclusive-scanned")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
 
@@ -241,7 +244,11 @@ def main():
 
     from flashlinear import LinearAttention
     from flashy_linear_attention_b200 import _lib, ops
-    from flashy_linear_attention_b200.sharding import shard_batch_heads
+    from flashy_linear_attention_b200.sharding import (
+        SequenceShardedLinearAttention,
+        exclusive_state_scan,
+        shard_batch_heads,
+    )
 
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
@@ -251,10 +258,15 @@ def main():
 
     B, H, N, dk, dv = WORKLOADS[args.workload]
     q, k, v, dy = make_inputs(B, H, N, dk, dv, device)
-    strong = args.scaling == "strong" and world > 1
-    if strong:
+    sharding = args.sharding or ("sequence" if args.workload == "cfg5" else "batch_head")
+    seq_sharded = sharding == "sequence" and world > 1
+    strong = (args.scaling == "strong" or seq_sharded) and world > 1
+    if seq_sharded:
+        lo, hi = rank * N // world, (rank + 1) * N // world
+        q, k, v, dy = (t[:, :, lo:hi].contiguous() for t in (q, k, v, dy))
+    elif strong:
         q, k, v, dy = (shard_batch_heads(t, rank, world).contiguous() for t in (q, k, v, dy))
-    Bl, Hl = q.shape[0], q.shape[1]
+    Bl, Hl, Nl = q.shape[0], q.shape[1], q.shape[2]
     global_batch = B if (strong or world == 1) else B * world
     torch.cuda.empty_cache()
     warmup = max(args.warmup, 3)
@@ -271,17 +283,39 @@ def main():
     # The forward also writes its final state (fp32, batch*heads x dk x dv) when the backward can
     # use it to sweep q, k, v, dO once -- what LinearAttention.apply + backward do.
     s_state = None
-    if ops.backward_uses_final_state(q, v):
+    if seq_sharded or ops.backward_uses_final_state(q, v):
         s_state = torch.empty(Bl * Hl, dk, dv, dtype=torch.float32, device=device)
+    seq_ctx = {}
+
+    def step_fwd():
+        if not seq_sharded:
+            ops.causal_dot_product_fwd(q, k, v, s_final=s_state)
+            return lib.fla_sm100_last_launch_count()
+        # sequence sharding: local state -> exclusive scan over ranks (one all-gather) -> forward
+        s_local = ops.chunk_state(k, v)
+        n = lib.fla_sm100_last_launch_count()
+        seq_ctx["prefix"] = exclusive_state_scan(s_local)
+        ops.causal_dot_product_fwd(q, k, v, s_init=seq_ctx["prefix"] if rank > 0 else None, s_final=s_state)
+        return n + lib.fla_sm100_last_launch_count()
+
+    def step_bwd():
+        if not seq_sharded:
+            ops.causal_dot_product_bwd(dy, q, k, v, s_last=s_state)
+            return lib.fla_sm100_last_launch_count()
+        r_local = ops.chunk_state(q, dy)
+        n = lib.fla_sm100_last_launch_count()
+        r_suffix = exclusive_state_scan(r_local, reverse=True)
+        ops.causal_dot_product_bwd(dy, q, k, v, s_init=seq_ctx["prefix"] if rank > 0 else None,
+                                   r_init=r_suffix if rank < world - 1 else None, s_last=s_state)
+        return n + lib.fla_sm100_last_launch_count()
+
     launches = 0
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     for _ in range(warmup):
-        ops.causal_dot_product_fwd(q, k, v, s_final=s_state)
-        launches_f = lib.fla_sm100_last_launch_count()
-        ops.causal_dot_product_bwd(dy, q, k, v, s_last=s_state)
-        launches_b = lib.fla_sm100_last_launch_count()
+        launches_f = step_fwd()
+        launches_b = step_bwd()
     barrier()
     ops.check_status(device)
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
@@ -289,9 +323,9 @@ def main():
     t_region0 = time.time()
     for i in range(steps):
         ev[i][0].record(stream)
-        ops.causal_dot_product_fwd(q, k, v, s_final=s_state)
+        step_fwd()
         ev[i][1].record(stream)
-        ops.causal_dot_product_bwd(dy, q, k, v, s_last=s_state)
+        step_bwd()
         ev[i][2].record(stream)
     barrier()
     clocks = sampler.stop(t_region0, time.time()) if rank == 0 else None
@@ -317,7 +351,10 @@ def main():
     def e2e_step():
         dq_, dk_, dv_, ddy = (x.to(device, non_blocking=True) for x in host_in)
         dq_.requires_grad_(True); dk_.requires_grad_(True); dv_.requires_grad_(True)
-        out = LinearAttention.apply(dq_, dk_, dv_)
+        if seq_sharded:
+            out = SequenceShardedLinearAttention.apply(dq_, dk_, dv_, None)
+        else:
+            out = LinearAttention.apply(dq_, dk_, dv_)
         grads = torch.autograd.grad(out, (dq_, dk_, dv_), ddy)
         for dst, src in zip(host_out, (out,) + tuple(grads)):
             dst.copy_(src.detach(), non_blocking=True)
@@ -341,7 +378,7 @@ def main():
 
     if rank == 0:
         peak, peak_src = measured_peaks()
-        fwd_b, bwd_b = algorithmic_bytes(Bl, Hl, N, dk, dv)  # this rank's share
+        fwd_b, bwd_b = algorithmic_bytes(Bl, Hl, Nl, dk, dv)  # this rank's share
         achieved = (fwd_b + bwd_b) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9
         traffic = NCU_TRAFFIC_BYTES_PER_STEP.get(args.workload) if world == 1 else None
         line = {
@@ -353,13 +390,17 @@ def main():
                 "workload": f"{args.workload}: LinearAttention fwd+bwd B={B} H={H} N={N} dk={dk} dv={dv} per "
                             f"{'job' if strong or world == 1 else 'GPU'}, q,k=elu(N(0,1))+1, v,dO~N(0,1), seed 0",
                 "global_batch": global_batch, "seq_len": N,
-                "parallelism": f"batch*head sharded over {world} GPU(s): {Bl}x{Hl} heads per GPU, no collective",
+                "parallelism": (f"sequence sharded over {world} GPUs: {Nl} tokens of every head per GPU, per-GPU "
+                                f"dk x dv fp32 states exclusive-scanned with one NCCL all-gather per pass")
+                if seq_sharded else
+                f"batch*head sharded over {world} GPU(s): {Bl}x{Hl} heads per GPU, no collective",
                 "l2": f"per-GPU working set {8 * q.numel() * 2 / 1e6:.0f} MB exceeds the 126 MB L2; no flush between steps",
                 "chunk": 128,
             },
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_all,
                     "d2h_bytes_per_step": d2h_all, "steps": e2e_steps,
-                    "api": "flashlinear.LinearAttention.apply + torch.autograd.grad, pinned host buffers"},
+                    "api": ("SequenceShardedLinearAttention.apply" if seq_sharded else
+                            "flashlinear.LinearAttention.apply") + " + torch.autograd.grad, pinned host buffers"},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {

@@ -17,6 +17,7 @@
 
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 namespace {
@@ -46,6 +47,23 @@ EncodeTiledFn get_encode_fn() {
 }
 
 thread_local int g_last_launches = 0;
+
+// FLA_DEBUG=1 in the environment: failed CUDA calls are described on stderr.
+bool debug_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("FLA_DEBUG");
+    return e != nullptr && e[0] == '1';
+  }();
+  return on;
+}
+#define FLA_LOG_FAILURE(...)                  \
+  do {                                        \
+    if (debug_enabled()) {                    \
+      fprintf(stderr, "[flashlinear_sm100] "); \
+      fprintf(stderr, __VA_ARGS__);           \
+      fprintf(stderr, "\n");                  \
+    }                                         \
+  } while (0)
 #ifdef FLA_TRACE
 long long* g_trace = nullptr;  // tracing build only: timeline buffer handed to every launch
 #endif
@@ -92,6 +110,11 @@ int encode_map(CUtensorMap* m, const Operand& o, int B, int H, int N, int box_ro
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(o.ptr), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    FLA_LOG_FAILURE("cuTensorMapEncodeTiled failed (%d): ptr %p dims %llu %llu %llu %llu strides %llu %llu %llu box %u",
+                    static_cast<int>(r), o.ptr, (unsigned long long)dims[0], (unsigned long long)dims[1],
+                    (unsigned long long)dims[2], (unsigned long long)dims[3], (unsigned long long)strides[0],
+                    (unsigned long long)strides[1], (unsigned long long)strides[2], box[1]);
   return r == CUDA_SUCCESS ? FLA_OK : FLA_ERR_CUDA;
 }
 
@@ -162,7 +185,17 @@ int device_info(DeviceInfo** out) {
   static DeviceInfo infos[64];
   static std::atomic<int> ready[64];
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FLA_ERR_CUDA;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    FLA_LOG_FAILURE("cudaGetDevice failed or device index %d out of range", dev);
+    return FLA_ERR_CUDA;
+  }
+  // Bind the device's primary context to THIS thread: cuTensorMapEncodeTiled is a driver call and
+  // needs a current context, which a thread that has only inherited the device index (an
+  // autograd worker, for one) does not have yet.
+  if (cudaSetDevice(dev) != cudaSuccess) {
+    FLA_LOG_FAILURE("cudaSetDevice(%d) failed", dev);
+    return FLA_ERR_CUDA;
+  }
   if (ready[dev].load(std::memory_order_acquire) != 2) {
     int expected = 0;
     if (ready[dev].compare_exchange_strong(expected, 1)) {
@@ -224,7 +257,11 @@ int launch_kernel(const KernelParams& kp_in, dim3 grid, cudaStream_t stream) {
 #endif
   fla::fla_chunk_kernel<D, D><<<grid, fla::kThreads, fla::Cfg<D, D>::SMEM_BYTES, stream>>>(kp);
   ++g_last_launches;
-  return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    FLA_LOG_FAILURE("launch of fla_chunk_kernel<%d> grid (%u,%u,%u) failed: %s", D, grid.x, grid.y,
+                    grid.z, cudaGetErrorString(e));
+  return e == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
 }
 
 int launch_template(int tmpl, const KernelParams& kp, dim3 grid, cudaStream_t stream) {
@@ -377,6 +414,9 @@ int run_state(const Operand& bop, const Operand& cop, int B, int H, int N, int d
 
 int check_common(const FlaArgs* a, DeviceInfo** dev) {
   if (a == nullptr) return FLA_ERR_INVALID;
+  // The launch checks below read the thread's last-error slot; drop whatever an earlier,
+  // unrelated call of this thread (another library's probe, for one) may have left in it.
+  (void)cudaGetLastError();
   if (a->batch <= 0 || a->heads <= 0 || a->seqlen <= 0 || a->dk <= 0 || a->dv <= 0)
     return FLA_ERR_INVALID;
   if (static_cast<long>(a->batch) * a->heads > 65535) return FLA_ERR_UNSUPPORTED;

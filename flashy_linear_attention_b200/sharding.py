@@ -67,18 +67,27 @@ class SequenceShardedLinearAttention(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx: Any, q, k, v, group=None):
+        rank = dist.get_rank(group)
         s_local = ops.chunk_state(k, v)
         s_prefix = exclusive_state_scan(s_local, group, reverse=False)
-        out = ops.causal_dot_product_fwd(q, k, v, s_init=s_prefix)
-        ctx.save_for_backward(q, k, v, s_prefix)
+        # The state after this shard's tokens lets the backward sweep its inputs once.
+        s_after = torch.empty_like(s_local)
+        out = ops.causal_dot_product_fwd(q, k, v, s_init=s_prefix if rank > 0 else None, s_final=s_after)
+        ctx.save_for_backward(q, k, v, s_prefix, s_after)
         ctx.group = group
         return out
 
     @staticmethod
     def backward(ctx: Any, grad_output) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, None]:
-        q, k, v, s_prefix = ctx.saved_tensors
+        q, k, v, s_prefix, s_after = ctx.saved_tensors
+        rank, world = dist.get_rank(ctx.group), dist.get_world_size(ctx.group)
         grad_output = grad_output.contiguous()
         r_local = ops.chunk_state(q, grad_output)
         r_suffix = exclusive_state_scan(r_local, ctx.group, reverse=True)
-        dq, dk, dv = ops.causal_dot_product_bwd(grad_output, q, k, v, s_init=s_prefix, r_init=r_suffix)
+        dq, dk, dv = ops.causal_dot_product_bwd(
+            grad_output, q, k, v,
+            s_init=s_prefix if rank > 0 else None,        # rank 0 starts the sequence: no prefix
+            r_init=r_suffix if rank < world - 1 else None,  # the last rank ends it: no suffix
+            s_last=s_after,
+        )
         return dq, dk, dv, None
