@@ -36,6 +36,7 @@ WORKLOADS = {
     "cfg3": (4, 32, 8192, 128, 128),
     "cfg3_small": (4, 32, 1024, 128, 128),  # cfg3's head count at N=1024: sized for ncu captures
     "cfg3_half": (4, 32, 4096, 128, 128),   # cfg3 at half the sequence length (1 GB resident)
+    "cfg4": (8, 16, 2048, 273, 64),  # LinearAttentionSmallVHD, 2nd-order Taylor features of 16 dims
     "cfg5": (1, 32, 65536, 128, 128),
 }
 METRIC = "fwd+bwd Mtokens/s, N=8K D=128 bf16, 1/2/4/8 B200; % tensor/HBM roofline"
@@ -140,8 +141,21 @@ class ClockSampler:
         }
 
 
+def taylor_features(x):
+    """[1, x / d^(1/4), vec(x x^T) / (sqrt(2) sqrt(d))] of raw x[..., d] (configuration 4)."""
+    d = x.shape[-1]
+    quad = (x.unsqueeze(-1) * x.unsqueeze(-2)).flatten(-2) / (2.0 ** 0.5 * d ** 0.5)
+    return torch.cat([torch.ones_like(x[..., :1]), x / d ** 0.25, quad], dim=-1)
+
+
 def make_inputs(B, H, N, dk, dv, device, seed=0):
     gen = torch.Generator(device=device).manual_seed(seed)
+    if dk == 273:  # second-order Taylor features of 16-dimensional raw q, k
+        q = taylor_features(torch.randn(B, H, N, 16, device=device, generator=gen)).to(torch.bfloat16)
+        k = taylor_features(torch.randn(B, H, N, 16, device=device, generator=gen)).to(torch.bfloat16)
+        v = torch.randn(B, H, N, dv, device=device, generator=gen).to(torch.bfloat16)
+        dy = torch.randn(B, H, N, dv, device=device, generator=gen).to(torch.bfloat16)
+        return q, k, v, dy
     q = (torch.nn.functional.elu(torch.randn(B, H, N, dk, device=device, generator=gen)) + 1).to(torch.bfloat16)
     k = (torch.nn.functional.elu(torch.randn(B, H, N, dk, device=device, generator=gen)) + 1).to(torch.bfloat16)
     v = torch.randn(B, H, N, dv, device=device, generator=gen).to(torch.bfloat16)
@@ -242,7 +256,7 @@ def main():
         raise SystemExit("bench.py: no CUDA device; the sm_100a kernels have no CPU fallback")
     import torch.distributed as dist
 
-    from flashlinear import LinearAttention
+    from flashlinear import LinearAttention, LinearAttentionSmallVHD
     from flashy_linear_attention_b200 import _lib, ops
     from flashy_linear_attention_b200.sharding import (
         SequenceShardedLinearAttention,
@@ -292,10 +306,12 @@ def main():
             ops.causal_dot_product_fwd(q, k, v, s_final=s_state)
             return lib.fla_sm100_last_launch_count()
         # sequence sharding: local state -> exclusive scan over ranks (one all-gather) -> forward
-        s_local = ops.chunk_state(k, v)
+        s_local, ws = ops.chunk_state(k, v, keep_workspace=True)
         n = lib.fla_sm100_last_launch_count()
         seq_ctx["prefix"] = exclusive_state_scan(s_local)
-        ops.causal_dot_product_fwd(q, k, v, s_init=seq_ctx["prefix"] if rank > 0 else None, s_final=s_state)
+        ops.causal_dot_product_fwd(q, k, v, s_init=seq_ctx["prefix"] if rank > 0 else None,
+                                   segment_workspace=ws if ws.numel() > 0 else None)
+        torch.add(seq_ctx["prefix"], s_local, out=s_state)  # state after this GPU's tokens
         return n + lib.fla_sm100_last_launch_count()
 
     def step_bwd():
@@ -354,7 +370,7 @@ def main():
         if seq_sharded:
             out = SequenceShardedLinearAttention.apply(dq_, dk_, dv_, None)
         else:
-            out = LinearAttention.apply(dq_, dk_, dv_)
+            out = (LinearAttentionSmallVHD if dk != dv else LinearAttention).apply(dq_, dk_, dv_)
         grads = torch.autograd.grad(out, (dq_, dk_, dv_), ddy)
         for dst, src in zip(host_out, (out,) + tuple(grads)):
             dst.copy_(src.detach(), non_blocking=True)
@@ -387,8 +403,11 @@ def main():
             "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {
-                "workload": f"{args.workload}: LinearAttention fwd+bwd B={B} H={H} N={N} dk={dk} dv={dv} per "
-                            f"{'job' if strong or world == 1 else 'GPU'}, q,k=elu(N(0,1))+1, v,dO~N(0,1), seed 0",
+                "workload": f"{args.workload}: {'LinearAttentionSmallVHD' if dk != dv else 'LinearAttention'} "
+                            f"fwd+bwd B={B} H={H} N={N} dk={dk} dv={dv} per "
+                            f"{'job' if strong or world == 1 else 'GPU'}, "
+                            + ("q,k=2nd-order Taylor features of N(0,1)^16" if dk == 273 else "q,k=elu(N(0,1))+1")
+                            + ", v,dO~N(0,1), seed 0",
                 "global_batch": global_batch, "seq_len": N,
                 "parallelism": (f"sequence sharded over {world} GPUs: {Nl} tokens of every head per GPU, per-GPU "
                                 f"dk x dv fp32 states exclusive-scanned with one NCCL all-gather per pass")

@@ -11,7 +11,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libflashlinear_sm100.so")
 
-FLA_ABI_VERSION = 2
+FLA_ABI_VERSION = 3
 
 
 class FlaTensor(ctypes.Structure):
@@ -44,6 +44,7 @@ class FlaArgs(ctypes.Structure):
         ("r_final", ctypes.c_void_p),
         ("s_last", ctypes.c_void_p),
         ("segments", ctypes.c_int32),
+        ("segment_states_ready", ctypes.c_int32),
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_size_t),
         ("status", ctypes.c_void_p),
@@ -60,6 +61,7 @@ EXPORTED_SYMBOLS = (
     "fla_sm100_bwd",
     "fla_sm100_state",
     "fla_sm100_fwd_static_scratch",
+    "fla_sm100_product",
     "fla_sm100_last_launch_count",
 )
 
@@ -92,6 +94,8 @@ def load() -> ctypes.CDLL:
     lib.fla_sm100_state.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_int]
     lib.fla_sm100_fwd_static_scratch.restype = ctypes.c_int
     lib.fla_sm100_fwd_static_scratch.argtypes = [ctypes.POINTER(FlaArgs)]
+    lib.fla_sm100_product.restype = ctypes.c_int
+    lib.fla_sm100_product.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_int]
     lib.fla_sm100_last_launch_count.restype = ctypes.c_int
     if lib.fla_sm100_abi_version() != FLA_ABI_VERSION:
         raise ImportError("libflashlinear_sm100.so has a different ABI version; rebuild it")

@@ -274,7 +274,7 @@ int launch_template(int tmpl, const KernelParams& kp, dim3 grid, cudaStream_t st
 // and a scan before it).
 int run_products(const Product* prods, int nprob, int B, int H, int N, int da, int dc,
                  int segments, void* workspace, size_t workspace_bytes, int32_t* status,
-                 cudaStream_t stream, const DeviceInfo& dev) {
+                 cudaStream_t stream, const DeviceInfo& dev, bool states_ready = false) {
   const int tmpl = pick_template(da, dc);
   if (tmpl == 0) return FLA_ERR_UNSUPPORTED;
   const int bh = B * H;
@@ -324,9 +324,21 @@ int run_products(const Product* prods, int nprob, int B, int H, int N, int da, i
     return launch_template(tmpl, kp, dim3(nprob, 1, bh), stream);
   }
 
+  float* ws = static_cast<float*>(workspace);
+  if (states_ready) {
+    // The caller ran the state pass already (fla_sm100_state): the workspace holds the segment
+    // prefixes of these tokens; the caller's initial state is added for every segment.
+    if (nprob != 1 || prods[0].ext_final != nullptr) return FLA_ERR_INVALID;
+    kp.prob[0].s_init = ws;
+    kp.prob[0].s_final = nullptr;
+    kp.prob[0].st_trans = 0;
+    kp.prob[0].s_add = prods[0].ext_init;
+    kp.prob[0].add_trans = prods[0].ext_trans;
+    kp.mode = 0;
+    return launch_template(tmpl, kp, dim3(1, nseg, bh), stream);
+  }
   // Pass A: per-segment sums of b^T c into the workspace (the last segment only when a final
   // state is wanted), exclusive scan over segments, then pass B with per-segment initial states.
-  float* ws = static_cast<float*>(workspace);
   ScanParams sp;
   memset(&sp, 0, sizeof(sp));
   for (int i = 0; i < nprob; ++i) {
@@ -528,7 +540,7 @@ int fla_sm100_fwd(const FlaArgs* a) {
   p.ext_trans = 0;
   return run_products(&p, 1, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->segments,
                       a->workspace, a->workspace_bytes, a->status,
-                      static_cast<cudaStream_t>(a->stream), *dev);
+                      static_cast<cudaStream_t>(a->stream), *dev, a->segment_states_ready != 0);
 }
 
 int fla_sm100_bwd(const FlaArgs* a) {
@@ -647,6 +659,25 @@ int fla_sm100_fwd_static_scratch(const FlaArgs* a) {
   return run_products(&p, 1, a->batch, a->heads, a->seqlen, a->dk, a->dv, nseg, scratch,
                       FLA_STATIC_SCRATCH_BYTES, a->status, static_cast<cudaStream_t>(a->stream),
                       *dev);
+}
+
+int fla_sm100_product(const FlaArgs* a, int anticausal) {
+  DeviceInfo* dev = nullptr;
+  g_last_launches = 0;
+  int rc = check_common(a, &dev);
+  if (rc) return rc;
+  Product p;
+  p.a = operand(a->q, a->dk);
+  p.b = operand(a->k, a->dk);
+  p.c = operand(a->v, a->dv);
+  p.out = operand(a->o, a->dv);
+  p.flags = anticausal ? (fla::kFlagDescending | fla::kFlagUpperMask) : 0;
+  p.ext_init = a->s_init;
+  p.ext_final = a->s_final;
+  p.ext_trans = 0;
+  return run_products(&p, 1, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->segments,
+                      a->workspace, a->workspace_bytes, a->status,
+                      static_cast<cudaStream_t>(a->stream), *dev);
 }
 
 }  // extern "C"

@@ -40,7 +40,8 @@ struct Problem {
   int flags;               // kFlag* bits below
   int st_trans;            // state arrays are stored transposed: element (row, col) at [col][row]
   int n_tokens;            // sequence length
-  int pad_;
+  int add_trans;           // layout of s_add: transposed like st_trans
+  const float* s_add;      // optional [bh][st_rows][st_cols] fp32 added to s_init for every segment
 };
 
 // Problem::flags
@@ -477,7 +478,13 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         for (int j = 0; j < 32; ++j) {
           const int col = cb * 32 + j;
           float x = 0.f;
-          if (row < p.st_rows && col < p.st_cols) x = src[st_off(row, col)];
+          if (row < p.st_rows && col < p.st_cols) {
+            x = src[st_off(row, col)];
+            if (pr.s_add != nullptr)
+              x += pr.s_add[static_cast<size_t>(bh) * st_elems +
+                            (pr.add_trans ? static_cast<size_t>(col) * p.st_rows + row
+                                          : static_cast<size_t>(row) * p.st_cols + col)];
+          }
           ra[j] = __float_as_uint(x);
         }
         ptx::tmem_st32(lane_base + cfg::S_COL + cb * 32, ra);

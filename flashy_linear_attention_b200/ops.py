@@ -17,7 +17,9 @@ import torch
 from . import _lib
 from ._lib import FlaArgs, FlaTensor
 
-MAX_HEAD_DIM = 128  # largest head dim the kernels are built for
+KERNEL_HEAD_DIM = 128  # widest head-dim tile of the kernels; wider dims are assembled from slices
+MAX_HEAD_DIM = 256     # cap of LinearAttention, as in the reference (linear_attn_kernels.py:322)
+MAX_HEAD_DIM_QK_SMALLV = 512  # cap of q/k for LinearAttentionSmallVHD (273-dim Taylor features fit)
 
 _status_words = {}
 
@@ -118,27 +120,70 @@ def _fptr(t: Optional[torch.Tensor], name: str, shape) -> Optional[int]:
     return t.data_ptr()
 
 
-def _call(pass_id: int, args: FlaArgs, device: torch.device, which: int = 0) -> None:
+def _call(pass_id: int, args: FlaArgs, device: torch.device, which: int = 0,
+          workspace: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """One C-ABI call on the current stream. Scratch comes from torch's allocator unless the
+    caller hands in `workspace`; the scratch tensor (or None) is returned."""
     lib = _lib.load()
     with torch.cuda.device(device):
         args.stream = torch.cuda.current_stream(device).cuda_stream
         args.status = _status_word(device).data_ptr()
-        need = lib.fla_sm100_workspace_bytes(ctypes.byref(args), pass_id)
-        ws = None
+        need = lib.fla_sm100_workspace_bytes(ctypes.byref(args), 0 if pass_id == 3 else pass_id)
+        ws = workspace
         if need > 0:
-            ws = torch.empty(need, dtype=torch.uint8, device=device)
+            if ws is None:
+                ws = torch.empty(need, dtype=torch.uint8, device=device)
+            elif ws.numel() * ws.element_size() < need:
+                raise ValueError("flashlinear: the workspace handed in is too small for this call")
             args.workspace = ws.data_ptr()
-            args.workspace_bytes = need
+            args.workspace_bytes = ws.numel() * ws.element_size()
         if pass_id == 0:
             rc = lib.fla_sm100_fwd(ctypes.byref(args))
         elif pass_id == 1:
             rc = lib.fla_sm100_bwd(ctypes.byref(args))
-        else:
+        elif pass_id == 2:
             rc = lib.fla_sm100_state(ctypes.byref(args), which)
+        else:
+            rc = lib.fla_sm100_product(ctypes.byref(args), which)
     if rc != 0:
         raise RuntimeError(f"flashlinear: libflashlinear_sm100 returned {rc}: {_lib.strerror(rc)}")
     if os.environ.get("FLA_DEBUG", "0") == "1":
         check_status(device)
+    return ws
+
+
+def _product_call(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, out: torch.Tensor, anticausal: bool) -> None:
+    """out = causal (or anti-causal) product of kernel-addressable views, head dims <= 128."""
+    B, H, N, da = a.shape
+    args = FlaArgs()
+    args.batch, args.heads, args.seqlen, args.dk, args.dv = B, H, N, da, c.shape[-1]
+    args.q, args.k, args.v, args.o = _desc(a), _desc(b), _desc(c), _desc(out)
+    _call(3, args, a.device, which=1 if anticausal else 0)
+
+
+def _product_sliced(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, like: torch.Tensor, anticausal: bool) -> torch.Tensor:
+    """Causal product for head dims above the kernels' 128-wide tiles, by linearity: output columns
+    are independent (slices of c), and (a_i . b_j) is the sum over slices of the a/b head dim, so
+    the partial products of those slices are added (fp32) before the one rounding to bf16."""
+    av, bv, cv = _kernel_view(a), _kernel_view(b), _kernel_view(c)
+    da, dc = a.shape[-1], c.shape[-1]
+    W = KERNEL_HEAD_DIM
+    out, ov = _out_like(like)
+    for c0 in range(0, dc, W):
+        c1 = min(dc, c0 + W)
+        if da <= W:
+            _product_call(av, bv, cv[..., c0:c1], ov[..., c0:c1], anticausal)
+            continue
+        acc = None
+        part = torch.empty(c.shape[:-1] + (c1 - c0,), dtype=c.dtype, device=c.device)
+        for a0 in range(0, da, W):
+            a1 = min(da, a0 + W)
+            _product_call(av[..., a0:a1], bv[..., a0:a1], cv[..., c0:c1], part, anticausal)
+            acc = part.float() if acc is None else acc + part.float()
+        ov[..., c0:c1] = acc.to(c.dtype)
+    if ov is not out:
+        out.copy_(ov)
+    return out
 
 
 def causal_dot_product_fwd(
@@ -148,15 +193,23 @@ def causal_dot_product_fwd(
     s_init: Optional[torch.Tensor] = None,
     s_final: Optional[torch.Tensor] = None,
     segments: int = 0,
+    segment_workspace: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """out[b,h,i] = sum_{j<=i} (q_i . k_j) v_j, bf16 in / bf16 out, fp32 accumulation.
 
     s_init / s_final are optional fp32 [batch*heads, dk, dv] running states (sum of k_j^T v_j
     before / after this call's tokens) for sequence-sharded or resumed calls.
+    segment_workspace: the scratch tensor returned by chunk_state(k, v, keep_workspace=True) for the
+    same k, v and `segments`; the call then reuses the segment states found there instead of
+    reading k, v once more to recompute them (s_final is not available in that case).
     """
     _check_inputs(q, k, v)
     B, H, N, dk = q.shape
     dv = v.shape[-1]
+    if dk > KERNEL_HEAD_DIM or dv > KERNEL_HEAD_DIM:
+        if s_init is not None or s_final is not None:
+            raise NotImplementedError("running-state arguments need head dims <= 128")
+        return _product_sliced(q, k, v, v, anticausal=False)
     qv, kv_, vv = _kernel_view(q), _kernel_view(k), _kernel_view(v)
     out, ov = _out_like(v)
     a = FlaArgs()
@@ -165,7 +218,11 @@ def causal_dot_product_fwd(
     a.s_init = _fptr(s_init, "s_init", (B * H, dk, dv))
     a.s_final = _fptr(s_final, "s_final", (B * H, dk, dv))
     a.segments = segments
-    _call(0, a, q.device)
+    if segment_workspace is not None:
+        if s_final is not None:
+            raise ValueError("flashlinear: s_final cannot be combined with segment_workspace")
+        a.segment_states_ready = 1
+    _call(0, a, q.device, workspace=segment_workspace)
     if ov is not out:
         out.copy_(ov)
     return out
@@ -189,6 +246,14 @@ def causal_dot_product_bwd(
     _check_inputs(grad_output, q, k, v)
     B, H, N, dk = q.shape
     dv = v.shape[-1]
+    if dk > KERNEL_HEAD_DIM or dv > KERNEL_HEAD_DIM:
+        if any(t is not None for t in (s_init, r_init, r_final, s_last)):
+            raise NotImplementedError("running-state arguments need head dims <= 128")
+        # the three gradients as products with permuted operands (see fla_sm100_product)
+        dQ = _product_sliced(grad_output, v, k, q, anticausal=False)
+        dV = _product_sliced(k, q, grad_output, v, anticausal=True)
+        dK = _product_sliced(v, grad_output, q, k, anticausal=True)
+        return dQ, dK, dV
     gv, qv, kv_, vv = (_kernel_view(t) for t in (grad_output, q, k, v))
     dQ, dQv = _out_like(q)
     dK, dKv = _out_like(k)
@@ -213,15 +278,19 @@ def backward_uses_final_state(q: torch.Tensor, v: torch.Tensor) -> bool:
     """True when the backward of this shape runs unsegmented, i.e. can take the forward's final
     state (`s_last`) and sweep q, k, v, dO once for all three gradients."""
     B, H, N, dk = q.shape
+    if dk > KERNEL_HEAD_DIM or v.shape[-1] > KERNEL_HEAD_DIM:
+        return False
     a = FlaArgs()
     a.batch, a.heads, a.seqlen, a.dk, a.dv = B, H, N, dk, v.shape[-1]
     with torch.cuda.device(q.device):
         return _lib.load().fla_sm100_auto_segments(ctypes.byref(a), 1) <= 1
 
 
-def chunk_state(b: torch.Tensor, c: torch.Tensor, segments: int = 0) -> torch.Tensor:
+def chunk_state(b: torch.Tensor, c: torch.Tensor, segments: int = 0, keep_workspace: bool = False):
     """fp32 [batch*heads, db, dc] sum over tokens of b_j^T c_j: with (k, v) the forward state S of
-    these tokens, with (q, dO) the backward state R. Used by sequence-sharded callers."""
+    these tokens, with (q, dO) the backward state R. Used by sequence-sharded callers.
+    keep_workspace=True returns (state, workspace): the scratch then holds the per-segment prefix
+    states, which causal_dot_product_fwd(..., segment_workspace=workspace) can reuse."""
     _check_inputs(b, c)
     B, H, N, db = b.shape
     dc = c.shape[-1]
@@ -232,7 +301,11 @@ def chunk_state(b: torch.Tensor, c: torch.Tensor, segments: int = 0) -> torch.Te
     a.k, a.v = _desc(bv), _desc(cv)
     a.s_final = out.data_ptr()
     a.segments = segments
-    _call(2, a, b.device, which=0)
+    ws = _call(2, a, b.device, which=0)
+    if keep_workspace:
+        if ws is None:  # unsegmented call: nothing to reuse, but keep the calling convention
+            ws = torch.empty(0, dtype=torch.uint8, device=b.device)
+        return out, ws
     return out
 
 
@@ -241,11 +314,11 @@ def chunk_state(b: torch.Tensor, c: torch.Tensor, segments: int = 0) -> torch.Te
 # ------------------------------------------------------------------------------------------------
 
 
-def _assert_shapes(hd_qk: int, sq: int) -> None:
-    # Same preconditions (and AssertionError) as the reference wrappers, with the head-dim cap of
-    # the kernels built here (linear_attn_kernels.py:322-325 asserts hd <= 256).
+def _assert_shapes(hd_qk: int, sq: int, cap: int = MAX_HEAD_DIM) -> None:
+    # Same preconditions (and AssertionError) as the reference wrappers
+    # (linear_attn_kernels.py:316-325: hd <= 256, sq a multiple of BLOCK_SQ = 64, or 32 above 128).
     block_sq = 64 if _next_pow2(hd_qk) <= 128 else 32
-    assert hd_qk <= MAX_HEAD_DIM, f"Only head_dims <= {MAX_HEAD_DIM} are supported."
+    assert hd_qk <= cap, f"Only head_dims <= {cap} are supported."
     assert (
         sq % block_sq == 0
     ), f"Number of elements in sequence must be a multiple of {block_sq}, {sq, block_sq}"
@@ -259,7 +332,9 @@ def check_forward_preconditions(q: torch.Tensor, v: torch.Tensor, smallv: bool) 
         assert _next_pow2(hd_v) <= _next_pow2(
             hd_qk
         ), "Value head dimension must be less than Query/Key head dimension."
-    _assert_shapes(hd_qk, sq)
+    # The reference caps hd_qk at 256 (linear_attn_kernels_smallv_hd.py:339); the cap is raised
+    # here so that 273-dimensional second-order Taylor features are accepted.
+    _assert_shapes(hd_qk, sq, MAX_HEAD_DIM_QK_SMALLV if smallv else MAX_HEAD_DIM)
 
 
 def linear_flash_wrapper_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
@@ -290,6 +365,6 @@ def linear_flash_wrapper_bwd_smallv_hd(
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Backward with separate q/k and v head dims (linear_attn_kernels_smallv_hd.py:363-405)."""
     batch, nh, sq, hd_qk = q.shape
-    assert hd_qk <= MAX_HEAD_DIM, f"Only head_dims <= {MAX_HEAD_DIM} are supported."
+    assert hd_qk <= MAX_HEAD_DIM_QK_SMALLV, f"Only head_dims <= {MAX_HEAD_DIM_QK_SMALLV} are supported."
     assert sq % 64 == 0, "Number of elements in sequence must be a multiple of 64"
     return causal_dot_product_bwd(grad_output, q, k, v)

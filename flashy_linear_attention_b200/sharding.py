@@ -68,11 +68,14 @@ class SequenceShardedLinearAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx: Any, q, k, v, group=None):
         rank = dist.get_rank(group)
-        s_local = ops.chunk_state(k, v)
+        # State pass first (its per-segment states stay in `ws` for the forward below), then the
+        # exchange of the per-GPU totals, then the forward on top of the received prefix.
+        s_local, ws = ops.chunk_state(k, v, keep_workspace=True)
         s_prefix = exclusive_state_scan(s_local, group, reverse=False)
+        out = ops.causal_dot_product_fwd(q, k, v, s_init=s_prefix if rank > 0 else None,
+                                         segment_workspace=ws if ws.numel() > 0 else None)
         # The state after this shard's tokens lets the backward sweep its inputs once.
-        s_after = torch.empty_like(s_local)
-        out = ops.causal_dot_product_fwd(q, k, v, s_init=s_prefix if rank > 0 else None, s_final=s_after)
+        s_after = s_prefix + s_local
         ctx.save_for_backward(q, k, v, s_prefix, s_after)
         ctx.group = group
         return out

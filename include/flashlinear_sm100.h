@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define FLA_ABI_VERSION 2
+#define FLA_ABI_VERSION 3
 
 enum {
   FLA_OK = 0,
@@ -85,6 +85,13 @@ typedef struct FlaArgs {
   /* Sequence segments per head (intra-GPU sequence split). 0 = pick automatically, 1 = none.
    * With more than one segment the call needs fla_sm100_workspace_bytes() of scratch. */
   int32_t segments;
+  /* Forward / product calls only, with more than one segment: non-zero means that `workspace`
+   * already holds the per-segment prefix states of these tokens, exactly as fla_sm100_state()
+   * left them there for the same k, v, shapes and `segments`. The call then skips its own state
+   * pass and scan, and s_init (if any) is added on top for every segment. This is how a
+   * sequence-sharded forward avoids reading k, v a third time: state pass -> exchange of the
+   * per-GPU totals -> this call. */
+  int32_t segment_states_ready;
 
   void* workspace;
   size_t workspace_bytes;
@@ -113,6 +120,15 @@ int fla_sm100_bwd(const FlaArgs* args);
  * calling fla_sm100_fwd / fla_sm100_bwd with s_init / r_init. The reference has no counterpart:
  * its kernels are quadratic and keep no state (flashlinear/kernels/linear_attn_kernels.py:63). */
 int fla_sm100_state(const FlaArgs* args, int which);
+
+/* The building block of both passes: o_i = sum_{j<=i} (q_i . k_j) v_j, or with anticausal != 0 the
+ * sum over j >= i (tokens walked from the last to the first; s_init / s_final then refer to the
+ * tokens after / up to this call's tokens). fla_sm100_fwd is this product of (q, k, v); the
+ * gradients of flashlinear/kernels/linear_attn_kernels.py:179-197 and :291-299 are
+ * dQ = product(dO, v, k), dV = anticausal product(k, q, dO), dK = anticausal product(v, dO, q).
+ * The Python layer uses it to assemble head dims above 128 from 128-wide slices. Workspace: as for
+ * pass 0. */
+int fla_sm100_product(const FlaArgs* args, int anticausal);
 
 /* Forward pass for callers that cannot obtain device memory themselves.
  * It has no counterpart in the reference (whose wrappers allocate through torch).

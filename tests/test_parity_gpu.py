@@ -138,6 +138,45 @@ def test_seeded_inputs_against_oracle(shape):
     _run_and_check(q, k, v, dy)
 
 
+@pytest.mark.parametrize("shape", [(1, 2, 256, 256, 256), (1, 2, 192, 200, 136), (2, 2, 256, 273, 64)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_head_dims_above_the_kernel_tile(shape):
+    """Head dims above 128 (the reference allows up to 256, flashlinear/kernels/
+    linear_attn_kernels.py:322; benchmark configuration 4 uses 273 Taylor features) are assembled
+    from 128-wide slices; same tolerance."""
+    B, H, N, dk, dv = shape
+    rng = np.random.default_rng(dk * 1000 + dv)
+    # scaled so that the scores stay O(1) at these widths
+    q = orc.bf16_round((orc.elu_plus_one(rng.standard_normal((B, H, N, dk))) / np.sqrt(dk)).astype(np.float32))
+    k = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, dk))).astype(np.float32))
+    v = orc.bf16_round(rng.standard_normal((B, H, N, dv)).astype(np.float32))
+    dy = orc.bf16_round(rng.standard_normal((B, H, N, dv)).astype(np.float32))
+    _run_and_check(q, k, v, dy)
+
+
+def test_taylor_feature_configuration_through_the_function():
+    """Benchmark configuration 4 in miniature: raw 16-dim q, k -> 273 second-order Taylor features
+    -> LinearAttentionSmallVHD with dv = 64, forward and backward, against the oracle."""
+    from flashlinear import LinearAttentionSmallVHD
+
+    rng = np.random.default_rng(4)
+    B, H, N = 1, 2, 384
+    q = orc.bf16_round(orc.taylor_feature_map(rng.standard_normal((B, H, N, 16))).astype(np.float32))
+    k = orc.bf16_round(orc.taylor_feature_map(rng.standard_normal((B, H, N, 16))).astype(np.float32))
+    v = orc.bf16_round(rng.standard_normal((B, H, N, 64)).astype(np.float32))
+    dy = orc.bf16_round(rng.standard_normal((B, H, N, 64)).astype(np.float32))
+    tq, tk, tv = (_to_dev(t).requires_grad_(True) for t in (q, k, v))
+    out = LinearAttentionSmallVHD.apply(tq, tk, tv)
+    out.backward(_to_dev(dy))
+    torch.cuda.synchronize()
+    q64, k64, v64, dy64 = (t.astype(np.float64) for t in (q, k, v, dy))
+    _check("out", _np(out), orc.linear_ref(q64, k64, v64))
+    rq, rk, rv = orc.linear_ref_grads(q64, k64, v64, dy64)
+    _check("dq", _np(tq.grad), rq)
+    _check("dk", _np(tk.grad), rk)
+    _check("dv", _np(tv.grad), rv)
+
+
 @pytest.mark.parametrize("segments", [2, 3, 8])
 def test_segmented_equals_oracle(segments):
     rng = np.random.default_rng(segments)
@@ -221,6 +260,31 @@ def test_running_state_arguments():
     for a, b, full_t in ((o1, o2, full), (dq1, dq2, fq), (dk1, dk2, fk), (dv1, dv2, fv)):
         got = torch.cat([a, b], dim=2)
         assert orc.frobenius_rel_error(_np(got), _np(full_t)) < 2e-3
+
+
+@pytest.mark.parametrize("segments", [1, 4])
+def test_forward_reuses_segment_states_of_the_state_pass(segments):
+    """chunk_state(keep_workspace) -> forward(segment_workspace, s_init): the sequence-sharded
+    forward's way of not reading k, v a third time. Must equal the plain forward with s_init."""
+    ops = _ops()
+    torch.manual_seed(3)
+    B, H, N, d = 1, 3, 2048, 128
+    q = torch.nn.functional.softplus(torch.randn(B, H, N, d, device=DEV)).to(torch.bfloat16)
+    k = torch.nn.functional.softplus(torch.randn(B, H, N, d, device=DEV)).to(torch.bfloat16)
+    v = torch.randn(B, H, N, d, device=DEV).to(torch.bfloat16)
+    prefix = torch.randn(B * H, d, d, device=DEV)
+    want = ops.causal_dot_product_fwd(q, k, v, s_init=prefix, segments=segments)
+    state, ws = ops.chunk_state(k, v, segments=segments, keep_workspace=True)
+    got = ops.causal_dot_product_fwd(q, k, v, s_init=prefix, segments=segments,
+                                     segment_workspace=ws if ws.numel() else None)
+    got0 = ops.causal_dot_product_fwd(q, k, v, segments=segments, segment_workspace=ws if ws.numel() else None)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    want_state = torch.matmul(k.float().transpose(-1, -2), v.float()).reshape(B * H, d, d)
+    assert (torch.linalg.norm(state - want_state) / torch.linalg.norm(want_state)).item() < 1e-4
+    assert (torch.linalg.norm(got.float() - want.float()) / torch.linalg.norm(want.float())).item() < 2e-3
+    plain = ops.causal_dot_product_fwd(q, k, v, segments=segments)
+    assert (torch.linalg.norm(got0.float() - plain.float()) / torch.linalg.norm(plain.float())).item() < 2e-3
 
 
 def test_strided_and_offset_inputs():
