@@ -65,7 +65,8 @@ bool debug_enabled() {
     }                                         \
   } while (0)
 #ifdef FLA_TRACE
-long long* g_trace = nullptr;  // tracing build only: timeline buffer handed to every launch
+long long* g_trace = nullptr;  // tracing build only: timeline buffer handed to launches of g_trace_mode
+int g_trace_mode = 0;
 #endif
 
 struct Operand {
@@ -128,8 +129,10 @@ struct Product {
 };
 
 // ---------------------------------------------------------------- segment state scan
-// ws: [prob][bh][seg][rows*cols] holds per-segment sums on entry and, on exit, the exclusive
-// prefix (in scan order) including the caller's initial state.
+// ws: [prob][bh][seg][cols][rows] holds per-segment sums on entry and, on exit, the exclusive
+// prefix (in scan order) including the caller's initial state. The scratch keeps every state
+// TRANSPOSED (column index slowest): the chunk kernel reads and writes states with one thread per
+// row, so consecutive lanes then touch consecutive addresses.
 struct ScanProblem {
   float* ws;
   const float* ext_init;
@@ -148,9 +151,9 @@ __global__ void fla_state_scan_kernel(const ScanParams sp) {
   const int elems = sp.rows * sp.cols;
   const int e = blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= elems) return;
-  const int row = e / sp.cols, col = e % sp.cols;
+  const int col = e / sp.rows, row = e % sp.rows;  // scratch layout [col][row]
   const size_t ext_idx = static_cast<size_t>(bh) * elems +
-                         (pr.ext_trans ? static_cast<size_t>(col) * sp.rows + row : e);
+                         (pr.ext_trans ? static_cast<size_t>(e) : static_cast<size_t>(row) * sp.cols + col);
   float run = pr.ext_init ? pr.ext_init[ext_idx] : 0.f;
   float* __restrict__ base = pr.ws + static_cast<size_t>(bh) * sp.nseg * elems + e;
   const int npresent = sp.have_last ? sp.nseg : sp.nseg - 1;  // segments whose sum was written
@@ -253,7 +256,7 @@ template <int D>
 int launch_kernel(const KernelParams& kp_in, dim3 grid, cudaStream_t stream) {
   KernelParams kp = kp_in;
 #ifdef FLA_TRACE
-  kp.trace = g_trace;
+  kp.trace = (kp.mode == g_trace_mode) ? g_trace : nullptr;
 #endif
   fla::fla_chunk_kernel<D, D><<<grid, fla::kThreads, fla::Cfg<D, D>::SMEM_BYTES, stream>>>(kp);
   ++g_last_launches;
@@ -331,7 +334,7 @@ int run_products(const Product* prods, int nprob, int B, int H, int N, int da, i
     if (nprob != 1 || prods[0].ext_final != nullptr) return FLA_ERR_INVALID;
     kp.prob[0].s_init = ws;
     kp.prob[0].s_final = nullptr;
-    kp.prob[0].st_trans = 0;
+    kp.prob[0].st_trans = 1;
     kp.prob[0].s_add = prods[0].ext_init;
     kp.prob[0].add_trans = prods[0].ext_trans;
     kp.mode = 0;
@@ -344,7 +347,7 @@ int run_products(const Product* prods, int nprob, int B, int H, int N, int da, i
   for (int i = 0; i < nprob; ++i) {
     kp.prob[i].s_init = nullptr;
     kp.prob[i].s_final = ws + i * ws_per_prob;
-    kp.prob[i].st_trans = 0;
+    kp.prob[i].st_trans = 1;  // scratch layout, see fla_state_scan_kernel
     sp.prob[i].ws = ws + i * ws_per_prob;
     sp.prob[i].ext_init = prods[i].ext_init;
     sp.prob[i].ext_final = prods[i].ext_final;
@@ -407,6 +410,7 @@ int run_state(const Operand& bop, const Operand& cop, int B, int H, int N, int d
   if ((rc = encode_map(&kp.prob[0].k, bop, B, H, N)) || (rc = encode_map(&kp.prob[0].v, cop, B, H, N)))
     return rc;
   kp.prob[0].s_final = (nseg == 1) ? final : static_cast<float*>(workspace);
+  kp.prob[0].st_trans = (nseg == 1) ? 0 : 1;  // the scratch keeps states transposed
   rc = launch_template(tmpl, kp, dim3(1, nseg, bh), stream);
   if (rc || nseg == 1) return rc;
   ScanParams sp;
@@ -482,7 +486,10 @@ extern "C" {
 int fla_sm100_abi_version(void) { return FLA_ABI_VERSION; }
 
 #ifdef FLA_TRACE
-void fla_sm100_set_trace(long long* buf) { g_trace = buf; }
+void fla_sm100_set_trace(long long* buf, int mode) {
+  g_trace = buf;
+  g_trace_mode = mode;
+}
 #endif
 
 const char* fla_sm100_strerror(int code) {

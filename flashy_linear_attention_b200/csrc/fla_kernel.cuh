@@ -208,10 +208,12 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
     ptx::prefetch_tensormap(&pr.k);
     ptx::prefetch_tensormap(&pr.v);
   }
+  FLA_TRACE_EVENT(31, 0);
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  FLA_TRACE_EVENT(31, 1);
 
   // Wait executed by a whole warp; the outcome is made uniform so that the warp never diverges
   // around .sync.aligned instructions.
@@ -345,7 +347,9 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       }
     } else {
       for (int i = 0; i < n_iter; ++i) {
+        FLA_TRACE_EVENT(0, i);
         if (!wait_tile(2 * i) || !wait_tile(2 * i + 1)) break;
+        FLA_TRACE_EVENT(4, i);
         const uint32_t k_lo = ptx::desc_lo(slot_addr(2 * i), kGroupBytes);
         const uint32_t v_lo = ptx::desc_lo(slot_addr(2 * i + 1), kGroupBytes);
         if (leader) {
@@ -446,7 +450,32 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         ptx::st_shared_v4(grp + (((j0 + jj) ^ swz) << 4), a0, a1, a2, a3);
       }
     };
+    // State arrays in the caller's layout ([row][col], col contiguous) are read and written
+    // through a per-warp 32x32 transpose in shared memory, so that global accesses are whole
+    // 128-byte row segments instead of one word per lane per line. (The transposed layout, used
+    // by the scratch, is coalesced as it is: consecutive lanes = consecutive rows.)
+    constexpr bool kStagedStateIO = (DK == 128);  // needs 8 x 4 KB of free shared memory
+    const uint32_t xpose_off = static_cast<uint32_t>(warp - 2) * 4096u;
+    auto xpose_addr = [&](uint32_t base, int j, int r) {  // element (col j, row r), XOR-swizzled
+      return base + xpose_off + static_cast<uint32_t>((j * 32 + (r ^ j)) * 4);
+    };
     auto write_final = [&](int cb, const uint32_t (&r)[32]) {
+      if (kStagedStateIO && !st_trans) {
+        const uint32_t base = sb_addr;  // the operand buffer is idle when a final state is written
+#pragma unroll
+        for (int j = 0; j < 32; ++j) ptx::st_shared_b32(xpose_addr(base, j, lane), r[j]);
+        __syncwarp();
+        const int col = cb * 32 + lane;
+#pragma unroll 4
+        for (int rr = 0; rr < 32; ++rr) {
+          const int grow = quad * 32 + rr;
+          const uint32_t x = ptx::ld_shared_b32(xpose_addr(base, lane, rr));
+          if (grow < p.st_rows && col < p.st_cols)
+            pr.s_final[st_index + static_cast<size_t>(grow) * p.st_cols + col] = __uint_as_float(x);
+        }
+        __syncwarp();
+        return;
+      }
       if (row < p.st_rows) {
 #pragma unroll
         for (int j = 0; j < 32; ++j)
@@ -474,18 +503,42 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
 #pragma unroll 1
       for (int jb = 0; jb < SBLK; ++jb) {
         const int cb = half * SBLK + jb;
+        // One 32-column block of a [st_rows][st_cols] state array (transposed storage if `trans`)
+        // into this thread's row registers; zero outside the valid part.
+        auto load_block = [&](const float* ptr, size_t index0, bool trans, uint32_t (&out)[32]) {
+          if (kStagedStateIO && !trans) {
+            const uint32_t base = ost_addr;  // the output staging buffer is idle before chunk 0
+            const int col = cb * 32 + lane;
+#pragma unroll 4
+            for (int rr = 0; rr < 32; ++rr) {
+              const int grow = quad * 32 + rr;
+              float x = 0.f;
+              if (grow < p.st_rows && col < p.st_cols)
+                x = ptr[index0 + static_cast<size_t>(grow) * p.st_cols + col];
+              ptx::st_shared_b32(xpose_addr(base, lane, rr), __float_as_uint(x));
+            }
+            __syncwarp();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int col = cb * 32 + j;
-          float x = 0.f;
-          if (row < p.st_rows && col < p.st_cols) {
-            x = src[st_off(row, col)];
-            if (pr.s_add != nullptr)
-              x += pr.s_add[static_cast<size_t>(bh) * st_elems +
-                            (pr.add_trans ? static_cast<size_t>(col) * p.st_rows + row
-                                          : static_cast<size_t>(row) * p.st_cols + col)];
+            for (int j = 0; j < 32; ++j) out[j] = ptx::ld_shared_b32(xpose_addr(base, j, lane));
+            __syncwarp();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = cb * 32 + j;
+              float x = 0.f;
+              if (row < p.st_rows && col < p.st_cols)
+                x = ptr[index0 + (trans ? static_cast<size_t>(col) * p.st_rows + row
+                                        : static_cast<size_t>(row) * p.st_cols + col)];
+              out[j] = __float_as_uint(x);
+            }
           }
-          ra[j] = __float_as_uint(x);
+        };
+        load_block(src, st_index, st_trans, ra);
+        if (pr.s_add != nullptr) {
+          load_block(pr.s_add, static_cast<size_t>(bh) * st_elems, pr.add_trans != 0, rb);
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            ra[j] = __float_as_uint(__uint_as_float(ra[j]) + __uint_as_float(rb[j]));
         }
         ptx::tmem_st32(lane_base + cfg::S_COL + cb * 32, ra);
         if (row < DK) store_sb(cb, ra);
@@ -494,6 +547,7 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before();
       ptx::mbar_arrive(sb_ready);
+      if (warp == 2) FLA_TRACE_EVENT(31, 2);
     }
 
     if (mode == 0) {
@@ -574,7 +628,8 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         if (!last || to_final) {
           ok = ptx::mbar_wait(s_full, i & 1, abort_flag) ? 1 : 0;
           // the state buffer is still the B operand of issuer Y's Q Sb of this chunk
-          if (ok && !last) ok = ptx::mbar_wait(qs_done, i & 1, abort_flag) ? 1 : 0;
+          // (also before a final-state write, which borrows that buffer as transpose scratch)
+          if (ok) ok = ptx::mbar_wait(qs_done, i & 1, abort_flag) ? 1 : 0;
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           if (warp == 2) FLA_TRACE_EVENT(14, i);
@@ -593,10 +648,12 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       // state only: one read-out after the last chunk
       int ok = ptx::mbar_wait(s_full, 0, abort_flag) ? 1 : 0;
       ok = __all_sync(0xffffffffu, ok);
+      if (warp == 2) FLA_TRACE_EVENT(31, 3);
       if (ok && pr.s_final != nullptr) {
         ptx::tc_fence_after();
         convert_state(false, true);
       }
+      if (warp == 2) FLA_TRACE_EVENT(31, 4);
     }
   } else {
     // ================================================================ epilogue group
@@ -665,6 +722,7 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
 
   // ------------------------------------------------------------------ teardown
   __syncwarp();
+  FLA_TRACE_EVENT(31, 5 + (warp < 15 ? warp : 0));
   if (*abort_flag) {
     // A wait gave up: let copies in flight land before the shared memory is released.
     __nanosleep(100000);
