@@ -241,6 +241,9 @@ def main():
     ap.add_argument("--sharding", default=None, choices=["batch_head", "sequence"],
                     help="N>1: batch_head (default) or sequence (default for cfg5): every GPU holds "
                          "N/W tokens of every head and the per-GPU states are exclusive-scanned")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="sequence sharding: peer = state kernels store straight into the peers' memory over "
+                         "NVLink and wait on flags (one fused kernel, no NCCL); nccl = all-gather + local sum")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
 
@@ -259,6 +262,8 @@ def main():
     from flashlinear import LinearAttention, LinearAttentionSmallVHD
     from flashy_linear_attention_b200 import _lib, ops
     from flashy_linear_attention_b200.sharding import (
+        PeerShardedLinearAttention,
+        PeerStateExchange,
         SequenceShardedLinearAttention,
         exclusive_state_scan,
         shard_batch_heads,
@@ -300,29 +305,42 @@ def main():
     if seq_sharded or ops.backward_uses_final_state(q, v):
         s_state = torch.empty(Bl * Hl, dk, dv, dtype=torch.float32, device=device)
     seq_ctx = {}
+    peer_ex = None
+    if seq_sharded and args.exchange == "peer":
+        peer_ex = PeerStateExchange(Bl, Hl, dk, dv, device)
 
     def step_fwd():
         if not seq_sharded:
             ops.causal_dot_product_fwd(q, k, v, s_final=s_state)
             return lib.fla_sm100_last_launch_count()
+        if peer_ex is not None:
+            # state pass + ONE kernel that scans, stores to the peers, waits and adds their totals
+            ws, seq_ctx["prefix"], seq_ctx["after"] = peer_ex.state_and_exchange(k, v, reverse=False)
+            n = lib.fla_sm100_last_launch_count()
+            ops.causal_dot_product_fwd(q, k, v, segment_workspace=ws)
+            return n + lib.fla_sm100_last_launch_count()
         # sequence sharding: local state -> exclusive scan over ranks (one all-gather) -> forward
         s_local, ws = ops.chunk_state(k, v, keep_workspace=True)
         n = lib.fla_sm100_last_launch_count()
         seq_ctx["prefix"] = exclusive_state_scan(s_local)
         ops.causal_dot_product_fwd(q, k, v, s_init=seq_ctx["prefix"] if rank > 0 else None,
                                    segment_workspace=ws if ws.numel() > 0 else None)
-        torch.add(seq_ctx["prefix"], s_local, out=s_state)  # state after this GPU's tokens
+        seq_ctx["after"] = torch.add(seq_ctx["prefix"], s_local, out=s_state)  # state after this GPU's tokens
         return n + lib.fla_sm100_last_launch_count()
 
     def step_bwd():
         if not seq_sharded:
             ops.causal_dot_product_bwd(dy, q, k, v, s_last=s_state)
             return lib.fla_sm100_last_launch_count()
-        r_local = ops.chunk_state(q, dy)
-        n = lib.fla_sm100_last_launch_count()
-        r_suffix = exclusive_state_scan(r_local, reverse=True)
+        if peer_ex is not None:
+            _, r_suffix, _ = peer_ex.state_and_exchange(q, dy, reverse=True)
+            n = lib.fla_sm100_last_launch_count()
+        else:
+            r_local = ops.chunk_state(q, dy)
+            n = lib.fla_sm100_last_launch_count()
+            r_suffix = exclusive_state_scan(r_local, reverse=True)
         ops.causal_dot_product_bwd(dy, q, k, v, s_init=seq_ctx["prefix"] if rank > 0 else None,
-                                   r_init=r_suffix if rank < world - 1 else None, s_last=s_state)
+                                   r_init=r_suffix if rank < world - 1 else None, s_last=seq_ctx["after"])
         return n + lib.fla_sm100_last_launch_count()
 
     launches = 0
@@ -367,7 +385,9 @@ def main():
     def e2e_step():
         dq_, dk_, dv_, ddy = (x.to(device, non_blocking=True) for x in host_in)
         dq_.requires_grad_(True); dk_.requires_grad_(True); dv_.requires_grad_(True)
-        if seq_sharded:
+        if seq_sharded and peer_ex is not None:
+            out = PeerShardedLinearAttention.apply(dq_, dk_, dv_, peer_ex)
+        elif seq_sharded:
             out = SequenceShardedLinearAttention.apply(dq_, dk_, dv_, None)
         else:
             out = (LinearAttentionSmallVHD if dk != dv else LinearAttention).apply(dq_, dk_, dv_)
@@ -409,8 +429,10 @@ def main():
                             + ("q,k=2nd-order Taylor features of N(0,1)^16" if dk == 273 else "q,k=elu(N(0,1))+1")
                             + ", v,dO~N(0,1), seed 0",
                 "global_batch": global_batch, "seq_len": N,
-                "parallelism": (f"sequence sharded over {world} GPUs: {Nl} tokens of every head per GPU, per-GPU "
-                                f"dk x dv fp32 states exclusive-scanned with one NCCL all-gather per pass")
+                "parallelism": (f"sequence sharded over {world} GPUs: {Nl} tokens of every head per GPU; per-GPU "
+                                f"dk x dv fp32 states exchanged "
+                                + ("by the state kernel itself (stores into the peers' HBM over NVLink + flags)"
+                                   if peer_ex is not None else "with one NCCL all-gather per pass"))
                 if seq_sharded else
                 f"batch*head sharded over {world} GPU(s): {Bl}x{Hl} heads per GPU, no collective",
                 "l2": f"per-GPU working set {8 * q.numel() * 2 / 1e6:.0f} MB exceeds the 126 MB L2; no flush between steps",
@@ -435,6 +457,8 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_sample(B, H, N, dk, dv)
         emit(line)
+    if peer_ex is not None:
+        peer_ex.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -11,7 +11,8 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libflashlinear_sm100.so")
 
-FLA_ABI_VERSION = 3
+FLA_ABI_VERSION = 4
+FLA_MAX_RANKS = 8
 
 
 class FlaTensor(ctypes.Structure):
@@ -52,6 +53,19 @@ class FlaArgs(ctypes.Structure):
     ]
 
 
+class FlaExchange(ctypes.Structure):
+    _fields_ = [
+        ("rank", ctypes.c_int32),
+        ("world", ctypes.c_int32),
+        ("reverse", ctypes.c_int32),
+        ("epoch", ctypes.c_uint32),
+        ("inbox", ctypes.c_void_p * 8),
+        ("flags", ctypes.c_void_p * 8),
+        ("remote_out", ctypes.c_void_p),
+        ("inclusive_out", ctypes.c_void_p),
+    ]
+
+
 EXPORTED_SYMBOLS = (
     "fla_sm100_abi_version",
     "fla_sm100_strerror",
@@ -62,6 +76,14 @@ EXPORTED_SYMBOLS = (
     "fla_sm100_state",
     "fla_sm100_fwd_static_scratch",
     "fla_sm100_product",
+    "fla_sm100_exchange_bytes",
+    "fla_sm100_exchange_workspace_bytes",
+    "fla_sm100_state_exchange",
+    "fla_sm100_enable_peer_access",
+    "fla_sm100_exchange_alloc",
+    "fla_sm100_exchange_open",
+    "fla_sm100_exchange_close",
+    "fla_sm100_exchange_free",
     "fla_sm100_last_launch_count",
 )
 
@@ -96,6 +118,23 @@ def load() -> ctypes.CDLL:
     lib.fla_sm100_fwd_static_scratch.argtypes = [ctypes.POINTER(FlaArgs)]
     lib.fla_sm100_product.restype = ctypes.c_int
     lib.fla_sm100_product.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_int]
+    lib.fla_sm100_exchange_bytes.restype = ctypes.c_int
+    lib.fla_sm100_exchange_bytes.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_int,
+                                             ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]
+    lib.fla_sm100_exchange_workspace_bytes.restype = ctypes.c_size_t
+    lib.fla_sm100_exchange_workspace_bytes.argtypes = [ctypes.POINTER(FlaArgs)]
+    lib.fla_sm100_exchange_alloc.restype = ctypes.c_int
+    lib.fla_sm100_exchange_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]
+    lib.fla_sm100_exchange_open.restype = ctypes.c_int
+    lib.fla_sm100_exchange_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
+    lib.fla_sm100_exchange_close.restype = ctypes.c_int
+    lib.fla_sm100_exchange_close.argtypes = [ctypes.c_void_p]
+    lib.fla_sm100_exchange_free.restype = ctypes.c_int
+    lib.fla_sm100_exchange_free.argtypes = [ctypes.c_void_p]
+    lib.fla_sm100_enable_peer_access.restype = ctypes.c_int
+    lib.fla_sm100_enable_peer_access.argtypes = [ctypes.c_int]
+    lib.fla_sm100_state_exchange.restype = ctypes.c_int
+    lib.fla_sm100_state_exchange.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_int, ctypes.POINTER(FlaExchange)]
     lib.fla_sm100_last_launch_count.restype = ctypes.c_int
     if lib.fla_sm100_abi_version() != FLA_ABI_VERSION:
         raise ImportError("libflashlinear_sm100.so has a different ABI version; rebuild it")

@@ -25,6 +25,10 @@ namespace {
 using fla::KernelParams;
 using fla::Problem;
 
+#ifndef FLA_L2_PROMOTION
+#define FLA_L2_PROMOTION CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+#endif
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -110,7 +114,7 @@ int encode_map(CUtensorMap* m, const Operand& o, int B, int H, int N, int box_ro
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(o.ptr), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  FLA_L2_PROMOTION, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     FLA_LOG_FAILURE("cuTensorMapEncodeTiled failed (%d): ptr %p dims %llu %llu %llu %llu strides %llu %llu %llu box %u",
                     static_cast<int>(r), o.ptr, (unsigned long long)dims[0], (unsigned long long)dims[1],
@@ -175,6 +179,107 @@ __global__ void fla_state_scan_kernel(const ScanParams sp) {
     }
   }
   if (pr.ext_final) pr.ext_final[ext_idx] = run;
+}
+
+// ---------------------------------------------------------------- scan fused with the exchange
+// Sequence sharding: the segment scan of one rank, the transfer of its total to every peer GPU
+// (stores into peer-mapped memory over NVLink), the bounded wait for the peers' totals and the
+// addition of the ones that precede (follow) this rank, all in one kernel. See FlaExchange in the
+// header. Inbox layout: [parity][source rank][bh][elems] (scratch layout), flags
+// [parity][source rank][block]; parity = epoch & 1.
+struct ExchangeParams {
+  float* ws;
+  int nseg, rows, cols, bh_count;
+  int rank, world, reverse;
+  unsigned epoch;
+  float* inbox[FLA_MAX_RANKS];
+  unsigned* flags[FLA_MAX_RANKS];
+  float* remote_out;
+  float* inclusive_out;
+  int* status;
+};
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__global__ void fla_state_exchange_kernel(const ExchangeParams xp) {
+  const int bh = blockIdx.y;
+  const int elems = xp.rows * xp.cols;
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  const bool active = e < elems;
+  const unsigned parity = xp.epoch & 1u;
+  const size_t nblocks = static_cast<size_t>(gridDim.x) * gridDim.y;
+  const size_t block_id = static_cast<size_t>(bh) * gridDim.x + blockIdx.x;
+  const size_t state_elems = static_cast<size_t>(xp.bh_count) * elems;
+  float* base = xp.ws + static_cast<size_t>(bh) * xp.nseg * elems + e;
+
+  // 1. this rank's total over its segments
+  float total = 0.f;
+  if (active) {
+    for (int g = 0; g < xp.nseg; ++g) total += __ldcg(base + static_cast<size_t>(g) * elems);
+  }
+  // 2. publish it: one store per peer into that peer's inbox slot for this rank
+  if (active) {
+    const size_t slot = (static_cast<size_t>(parity) * xp.world + xp.rank) * state_elems +
+                        static_cast<size_t>(bh) * elems + e;
+    for (int d = 0; d < xp.world; ++d)
+      if (d != xp.rank) xp.inbox[d][slot] = total;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const size_t f = (static_cast<size_t>(parity) * xp.world + xp.rank) * nblocks + block_id;
+    for (int d = 0; d < xp.world; ++d)
+      if (d != xp.rank) st_release_sys(xp.flags[d] + f, xp.epoch);
+  }
+  // 3. wait (bounded) for the same block of every other rank. Waiting for all of them, not only the
+  //    ones whose totals are needed, keeps any rank from running two exchanges ahead of another,
+  //    which is what makes two parity buffers enough.
+  __shared__ int timed_out;
+  if (threadIdx.x == 0) timed_out = 0;
+  __syncthreads();
+  if (threadIdx.x < xp.world && static_cast<int>(threadIdx.x) != xp.rank) {
+    const unsigned* f = xp.flags[xp.rank] +
+                        (static_cast<size_t>(parity) * xp.world + threadIdx.x) * nblocks + block_id;
+    const long long t0 = clock64();
+    while (ld_acquire_sys(f) != xp.epoch) {
+      if (clock64() - t0 > fla::ptx::kWaitLimitCycles) {
+        timed_out = 1;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (timed_out) {
+    if (threadIdx.x == 0 && xp.status != nullptr) atomicOr(xp.status, 2);
+    return;
+  }
+  if (!active) return;
+  // 4. totals of the ranks before (after) this one, from this GPU's own inbox
+  float remote = 0.f;
+  const int lo = xp.reverse ? xp.rank + 1 : 0;
+  const int hi = xp.reverse ? xp.world : xp.rank;
+  for (int s = lo; s < hi; ++s)
+    remote += __ldcg(xp.inbox[xp.rank] + (static_cast<size_t>(parity) * xp.world + s) * state_elems +
+                     static_cast<size_t>(bh) * elems + e);
+  // 5. segment prefixes on top of it
+  float run = remote;
+  for (int g = 0; g < xp.nseg; ++g) {
+    float* p = base + static_cast<size_t>(g) * elems;
+    const float local = __ldcg(p);
+    *p = run;
+    run += local;
+  }
+  const int col = e / xp.rows, row = e % xp.rows;  // scratch layout [col][row] -> caller [row][col]
+  const size_t ext_idx = static_cast<size_t>(bh) * elems + static_cast<size_t>(row) * xp.cols + col;
+  if (xp.remote_out) xp.remote_out[ext_idx] = remote;
+  if (xp.inclusive_out) xp.inclusive_out[ext_idx] = run;
 }
 
 // ---------------------------------------------------------------- launch plumbing
@@ -317,6 +422,23 @@ int run_products(const Product* prods, int nprob, int B, int H, int N, int da, i
     want_final |= (pd.ext_final != nullptr);
   }
 
+  if (states_ready) {
+    // The caller ran the state pass already (fla_sm100_state / fla_sm100_state_exchange): the
+    // workspace holds the segment prefixes of these tokens, in the scratch layout; the caller's
+    // initial state, if any, is added for every segment.
+    if (nprob != 1 || prods[0].ext_final != nullptr) return FLA_ERR_INVALID;
+    if (workspace == nullptr ||
+        workspace_bytes < static_cast<size_t>(bh) * nseg * da * dc * sizeof(float))
+      return FLA_ERR_WORKSPACE;
+    kp.prob[0].s_init = static_cast<float*>(workspace);
+    kp.prob[0].s_final = nullptr;
+    kp.prob[0].st_trans = 1;
+    kp.prob[0].s_add = prods[0].ext_init;
+    kp.prob[0].add_trans = prods[0].ext_trans;
+    kp.mode = 0;
+    return launch_template(tmpl, kp, dim3(1, nseg, bh), stream);
+  }
+
   if (nseg == 1) {
     for (int i = 0; i < nprob; ++i) {
       kp.prob[i].s_init = prods[i].ext_init;
@@ -328,18 +450,6 @@ int run_products(const Product* prods, int nprob, int B, int H, int N, int da, i
   }
 
   float* ws = static_cast<float*>(workspace);
-  if (states_ready) {
-    // The caller ran the state pass already (fla_sm100_state): the workspace holds the segment
-    // prefixes of these tokens; the caller's initial state is added for every segment.
-    if (nprob != 1 || prods[0].ext_final != nullptr) return FLA_ERR_INVALID;
-    kp.prob[0].s_init = ws;
-    kp.prob[0].s_final = nullptr;
-    kp.prob[0].st_trans = 1;
-    kp.prob[0].s_add = prods[0].ext_init;
-    kp.prob[0].add_trans = prods[0].ext_trans;
-    kp.mode = 0;
-    return launch_template(tmpl, kp, dim3(1, nseg, bh), stream);
-  }
   // Pass A: per-segment sums of b^T c into the workspace (the last segment only when a final
   // state is wanted), exclusive scan over segments, then pass B with per-segment initial states.
   ScanParams sp;
@@ -685,6 +795,184 @@ int fla_sm100_product(const FlaArgs* a, int anticausal) {
   return run_products(&p, 1, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->segments,
                       a->workspace, a->workspace_bytes, a->status,
                       static_cast<cudaStream_t>(a->stream), *dev);
+}
+
+namespace {
+// Segment count and scratch size of the exchange path (scratch is needed even for one segment).
+int exchange_segments(const FlaArgs* a, int sm_count) {
+  const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
+  int nseg = a->segments > 0 ? a->segments : auto_segments(1, a->batch * a->heads, nchunks, sm_count);
+  if (nseg > nchunks) nseg = nchunks;
+  if (nseg < 1) nseg = 1;
+  const int seg_chunks = (nchunks + nseg - 1) / nseg;
+  return (nchunks + seg_chunks - 1) / seg_chunks;
+}
+int current_sm_count() {
+  int sm = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev);
+  return sm;
+}
+}  // namespace
+
+size_t fla_sm100_exchange_workspace_bytes(const FlaArgs* a) {
+  if (a == nullptr) return 0;
+  const int nseg = exchange_segments(a, current_sm_count());
+  // (the slack matches fla_sm100_workspace_bytes, so that one buffer serves both calls)
+  return static_cast<size_t>(a->batch) * a->heads * nseg * a->dk * a->dv * sizeof(float) + 1024;
+}
+
+int fla_sm100_enable_peer_access(int peer_device) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return FLA_ERR_CUDA;
+  if (peer_device == dev) return FLA_OK;
+  int can = 0;
+  if (cudaDeviceCanAccessPeer(&can, dev, peer_device) != cudaSuccess || !can) {
+    FLA_LOG_FAILURE("device %d cannot access peer %d", dev, peer_device);
+    return FLA_ERR_DEVICE;
+  }
+  const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    (void)cudaGetLastError();
+    return FLA_OK;
+  }
+  if (e != cudaSuccess) FLA_LOG_FAILURE("cudaDeviceEnablePeerAccess(%d) failed: %s", peer_device, cudaGetErrorString(e));
+  return e == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
+
+// Exchange buffers are allocated by the library itself (plain cudaMalloc, zero-filled) so that
+// their CUDA IPC handles refer to whole allocations, and a peer opens them with ITS OWN device
+// current: an import made under another device's context is not reachable from this device's
+// kernels, peer access or not.
+int fla_sm100_exchange_alloc(size_t bytes, void** ptr, unsigned char* handle64) {
+  if (ptr == nullptr || handle64 == nullptr || bytes == 0) return FLA_ERR_INVALID;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e == cudaSuccess) e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    FLA_LOG_FAILURE("exchange_alloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+    if (p) cudaFree(p);
+    return FLA_ERR_CUDA;
+  }
+  memcpy(handle64, &h, 64);
+  *ptr = p;
+  return FLA_OK;
+}
+
+int fla_sm100_exchange_open(const unsigned char* handle64, void** ptr) {
+  if (ptr == nullptr || handle64 == nullptr) return FLA_ERR_INVALID;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    FLA_LOG_FAILURE("cudaIpcOpenMemHandle failed: %s", cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return FLA_ERR_CUDA;
+  }
+  // Check the mapping with a runtime copy (an error code, not a device fault, if it is unusable).
+  unsigned probe = 0;
+  e = cudaMemcpy(&probe, p, sizeof(probe), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess) e = cudaMemcpy(p, &probe, sizeof(probe), cudaMemcpyHostToDevice);  // same value back
+  if (e != cudaSuccess) {
+    FLA_LOG_FAILURE("peer mapping is not readable / writable: %s", cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    cudaIpcCloseMemHandle(p);
+    return FLA_ERR_CUDA;
+  }
+  *ptr = p;
+  return FLA_OK;
+}
+
+int fla_sm100_exchange_close(void* ptr) {
+  return (ptr != nullptr && cudaIpcCloseMemHandle(ptr) == cudaSuccess) ? FLA_OK : FLA_ERR_CUDA;
+}
+
+int fla_sm100_exchange_free(void* ptr) {
+  return (ptr != nullptr && cudaFree(ptr) == cudaSuccess) ? FLA_OK : FLA_ERR_CUDA;
+}
+
+int fla_sm100_exchange_bytes(const FlaArgs* a, int world, size_t* inbox_bytes, size_t* flag_bytes) {
+  if (a == nullptr || world < 1 || world > FLA_MAX_RANKS) return FLA_ERR_INVALID;
+  const size_t bh = static_cast<size_t>(a->batch) * a->heads;
+  const size_t elems = static_cast<size_t>(a->dk) * a->dv;
+  const size_t nblocks = bh * ((elems + 255) / 256);
+  if (inbox_bytes) *inbox_bytes = 2 * static_cast<size_t>(world) * bh * elems * sizeof(float);
+  if (flag_bytes) *flag_bytes = 2 * static_cast<size_t>(world) * nblocks * sizeof(unsigned);
+  return FLA_OK;
+}
+
+int fla_sm100_state_exchange(const FlaArgs* a, int which, const FlaExchange* x) {
+  DeviceInfo* dev = nullptr;
+  g_last_launches = 0;
+  int rc = check_common(a, &dev);
+  if (rc) return rc;
+  if (x == nullptr || x->world < 1 || x->world > FLA_MAX_RANKS || x->rank < 0 ||
+      x->rank >= x->world || x->epoch == 0 || (which != 0 && which != 1))
+    return FLA_ERR_INVALID;
+  for (int d = 0; d < x->world; ++d)
+    if (x->inbox[d] == nullptr || x->flags[d] == nullptr) return FLA_ERR_INVALID;
+  const Operand bop = which == 0 ? operand(a->k, a->dk) : operand(a->q, a->dk);
+  const Operand cop = which == 0 ? operand(a->v, a->dv) : operand(a->d_o, a->dv);
+  const int da = a->dk, dc = a->dv;
+  const int tmpl = pick_template(da, dc);
+  if (tmpl == 0) return FLA_ERR_UNSUPPORTED;
+  if ((rc = check_operand(bop, a->batch, a->heads)) || (rc = check_operand(cop, a->batch, a->heads)))
+    return rc;
+  const int bh = a->batch * a->heads;
+  const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
+  const int nseg = exchange_segments(a, dev->sm_count);
+  const int seg_chunks = (nchunks + nseg - 1) / nseg;
+  const size_t need = static_cast<size_t>(bh) * nseg * da * dc * sizeof(float);
+  if (a->workspace == nullptr || a->workspace_bytes < need) return FLA_ERR_WORKSPACE;
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+
+  // state pass: every segment's sum of b^T c into the scratch (scratch layout)
+  KernelParams kp;
+  memset(&kp, 0, sizeof(kp));
+  kp.heads = a->heads;
+  kp.nchunks = nchunks;
+  kp.seg_chunks = seg_chunks;
+  kp.st_rows = da;
+  kp.st_cols = dc;
+  kp.status = a->status;
+  kp.mode = 1;
+  if ((rc = encode_map(&kp.prob[0].k, bop, a->batch, a->heads, a->seqlen)) ||
+      (rc = encode_map(&kp.prob[0].v, cop, a->batch, a->heads, a->seqlen)))
+    return rc;
+  kp.prob[0].s_final = static_cast<float*>(a->workspace);
+  kp.prob[0].st_trans = 1;
+  kp.prob[0].flags = x->reverse ? (fla::kFlagDescending | fla::kFlagUpperMask) : 0;
+  if ((rc = launch_template(tmpl, kp, dim3(1, nseg, bh), stream))) return rc;
+
+  // scan + publish to the peers + bounded wait + add the peers' totals
+  ExchangeParams xp;
+  memset(&xp, 0, sizeof(xp));
+  xp.ws = static_cast<float*>(a->workspace);
+  xp.nseg = nseg;
+  xp.rows = da;
+  xp.cols = dc;
+  xp.bh_count = bh;
+  xp.rank = x->rank;
+  xp.world = x->world;
+  xp.reverse = x->reverse;
+  xp.epoch = x->epoch;
+  for (int d = 0; d < x->world; ++d) {
+    xp.inbox[d] = x->inbox[d];
+    xp.flags[d] = x->flags[d];
+  }
+  xp.remote_out = x->remote_out;
+  xp.inclusive_out = x->inclusive_out;
+  xp.status = a->status;
+  const int elems = da * dc;
+  fla_state_exchange_kernel<<<dim3((elems + 255) / 256, bh, 1), 256, 0, stream>>>(xp);
+  ++g_last_launches;
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) FLA_LOG_FAILURE("launch of fla_state_exchange_kernel failed: %s", cudaGetErrorString(e));
+  return e == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
 }
 
 }  // extern "C"

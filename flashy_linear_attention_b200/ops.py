@@ -130,13 +130,15 @@ def _call(pass_id: int, args: FlaArgs, device: torch.device, which: int = 0,
         args.status = _status_word(device).data_ptr()
         need = lib.fla_sm100_workspace_bytes(ctypes.byref(args), 0 if pass_id == 3 else pass_id)
         ws = workspace
-        if need > 0:
-            if ws is None:
-                ws = torch.empty(need, dtype=torch.uint8, device=device)
-            elif ws.numel() * ws.element_size() < need:
+        if ws is not None:
+            if ws.numel() * ws.element_size() < need:
                 raise ValueError("flashlinear: the workspace handed in is too small for this call")
             args.workspace = ws.data_ptr()
             args.workspace_bytes = ws.numel() * ws.element_size()
+        elif need > 0:
+            ws = torch.empty(need, dtype=torch.uint8, device=device)
+            args.workspace = ws.data_ptr()
+            args.workspace_bytes = need
         if pass_id == 0:
             rc = lib.fla_sm100_fwd(ctypes.byref(args))
         elif pass_id == 1:

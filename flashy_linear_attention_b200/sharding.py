@@ -13,12 +13,14 @@ Two partitionings (the reference has neither; its launch grid is a single GPU's
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Any, Optional, Tuple
 
 import torch
 import torch.distributed as dist
 
-from . import ops
+from . import _lib, ops
+from ._lib import FlaArgs, FlaExchange
 
 
 def shard_batch_heads(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
@@ -91,6 +93,145 @@ class SequenceShardedLinearAttention(torch.autograd.Function):
             grad_output, q, k, v,
             s_init=s_prefix if rank > 0 else None,        # rank 0 starts the sequence: no prefix
             r_init=r_suffix if rank < world - 1 else None,  # the last rank ends it: no suffix
+            s_last=s_after,
+        )
+        return dq, dk, dv, None
+
+
+class PeerStateExchange:
+    """State exchange of sequence sharding over peer-mapped memory instead of NCCL.
+
+    Every rank owns an inbox and a flag array in its own HBM; the other ranks of the node map them
+    through CUDA IPC. `state_and_exchange()` then runs the state pass and ONE kernel that scans the
+    segment states, stores this rank's total into every peer's inbox over NVLink, waits (bounded)
+    for the peers' totals and folds the ones that precede (follow) this rank into the segment
+    prefixes -- see fla_sm100_state_exchange in include/flashlinear_sm100.h.
+    All ranks must call it the same number of times in the same order."""
+
+    def __init__(self, batch: int, heads: int, dk: int, dv: int, device: torch.device,
+                 group: Optional[dist.ProcessGroup] = None):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if self.world > _lib.FLA_MAX_RANKS:
+            raise ValueError(f"PeerStateExchange supports up to {_lib.FLA_MAX_RANKS} ranks")
+        self.device = device
+        self.shape = (batch, heads, dk, dv)
+        self._lib = lib = _lib.load()
+        a = FlaArgs()
+        a.batch, a.heads, a.seqlen, a.dk, a.dv = batch, heads, 128, dk, dv
+        inbox_b, flag_b = ctypes.c_size_t(0), ctypes.c_size_t(0)
+        rc = lib.fla_sm100_exchange_bytes(ctypes.byref(a), self.world, ctypes.byref(inbox_b), ctypes.byref(flag_b))
+        if rc != 0:
+            raise RuntimeError(_lib.strerror(rc))
+        self._owned, self._opened = [], []
+        # one buffer set per direction (forward states / backward states), each with its own epoch
+        self._sets = []
+        with torch.cuda.device(device):
+            for _ in range(2):
+                mine = []
+                for nbytes in (inbox_b.value, flag_b.value):
+                    ptr = ctypes.c_void_p()
+                    handle = ctypes.create_string_buffer(64)
+                    rc = lib.fla_sm100_exchange_alloc(nbytes, ctypes.byref(ptr), handle)
+                    if rc != 0:
+                        raise RuntimeError(f"flashlinear: exchange buffer allocation: {_lib.strerror(rc)}")
+                    self._owned.append(ptr.value)
+                    mine.append((ptr.value, handle.raw))
+                gathered = [None] * self.world
+                dist.all_gather_object(gathered, (self.rank, mine[0][1], mine[1][1]), group=group)
+                inbox_ptrs, flag_ptrs = [0] * self.world, [0] * self.world
+                for r, h_inbox, h_flags in gathered:
+                    if r == self.rank:
+                        inbox_ptrs[r], flag_ptrs[r] = mine[0][0], mine[1][0]
+                        continue
+                    for dst, h in ((inbox_ptrs, h_inbox), (flag_ptrs, h_flags)):
+                        ptr = ctypes.c_void_p()
+                        # opened with THIS rank's device current: its kernels store into the peer
+                        rc = lib.fla_sm100_exchange_open(h, ctypes.byref(ptr))
+                        if rc != 0:
+                            raise RuntimeError(f"flashlinear: mapping rank {r}'s exchange buffer: {_lib.strerror(rc)}")
+                        self._opened.append(ptr.value)
+                        dst[r] = ptr.value
+                self._sets.append({"inbox": inbox_ptrs, "flags": flag_ptrs, "epoch": 0})
+        dist.barrier(group=group)
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers and frees this rank's (call on every rank, after a barrier)."""
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            for p in self._opened:
+                self._lib.fla_sm100_exchange_close(p)
+            self._opened = []
+            if dist.is_initialized():
+                dist.barrier(group=self.group)  # nobody frees memory a peer still has mapped
+            for p in self._owned:
+                self._lib.fla_sm100_exchange_free(p)
+            self._owned = []
+
+    def state_and_exchange(self, b: torch.Tensor, c: torch.Tensor, reverse: bool, segments: int = 0):
+        """States of this rank's tokens (sum b^T c), exchanged. Returns (workspace, remote, inclusive):
+        the scratch with the per-segment prefixes (for segment_workspace=...), the fp32
+        [batch*heads, db, dc] sum over the ranks before (after, if reverse) this one, and that sum
+        plus this rank's own total."""
+        ops._check_inputs(b, c)
+        B, H, N, db = b.shape
+        dc = c.shape[-1]
+        if (B, H, db, dc) != self.shape:
+            raise ValueError("PeerStateExchange was created for another shape")
+        lib = _lib.load()
+        bset = self._sets[1 if reverse else 0]
+        bset["epoch"] += 1
+        bv, cv = ops._kernel_view(b), ops._kernel_view(c)
+        remote = torch.empty(B * H, db, dc, dtype=torch.float32, device=b.device)
+        inclusive = torch.empty_like(remote)
+        a = FlaArgs()
+        a.batch, a.heads, a.seqlen, a.dk, a.dv = B, H, N, db, dc
+        # operands go where fla_sm100_state_exchange(which) reads them: which=0 reads k, v
+        a.k, a.v = ops._desc(bv), ops._desc(cv)
+        a.segments = segments
+        x = FlaExchange()
+        x.rank, x.world, x.reverse, x.epoch = self.rank, self.world, 1 if reverse else 0, bset["epoch"]
+        for r in range(self.world):
+            x.inbox[r] = bset["inbox"][r]
+            x.flags[r] = bset["flags"][r]
+        x.remote_out = remote.data_ptr()
+        x.inclusive_out = inclusive.data_ptr()
+        with torch.cuda.device(b.device):
+            need = lib.fla_sm100_exchange_workspace_bytes(ctypes.byref(a))
+            ws = torch.empty(need, dtype=torch.uint8, device=b.device)
+            a.workspace, a.workspace_bytes = ws.data_ptr(), need
+            a.stream = torch.cuda.current_stream(b.device).cuda_stream
+            a.status = ops._status_word(b.device).data_ptr()
+            rc = lib.fla_sm100_state_exchange(ctypes.byref(a), 0, ctypes.byref(x))
+        if rc != 0:
+            raise RuntimeError(f"flashlinear: fla_sm100_state_exchange returned {rc}: {_lib.strerror(rc)}")
+        return ws, remote, inclusive
+
+
+class PeerShardedLinearAttention(torch.autograd.Function):
+    """SequenceShardedLinearAttention with the exchange fused into the state kernels
+    (`apply(q, k, v, exchange)` with a PeerStateExchange made for these shapes)."""
+
+    @staticmethod
+    def forward(ctx: Any, q, k, v, exchange: PeerStateExchange):
+        ws, s_prefix, s_after = exchange.state_and_exchange(k, v, reverse=False)
+        # the scratch already holds prefix-of-other-ranks + local segment prefixes
+        out = ops.causal_dot_product_fwd(q, k, v, segment_workspace=ws)
+        ctx.save_for_backward(q, k, v, s_prefix, s_after)
+        ctx.exchange = exchange
+        return out
+
+    @staticmethod
+    def backward(ctx: Any, grad_output):
+        q, k, v, s_prefix, s_after = ctx.saved_tensors
+        ex = ctx.exchange
+        grad_output = grad_output.contiguous()
+        _, r_suffix, _ = ex.state_and_exchange(q, grad_output, reverse=True)
+        dq, dk, dv = ops.causal_dot_product_bwd(
+            grad_output, q, k, v,
+            s_init=s_prefix if ex.rank > 0 else None,
+            r_init=r_suffix if ex.rank < ex.world - 1 else None,
             s_last=s_after,
         )
         return dq, dk, dv, None

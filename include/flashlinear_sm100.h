@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define FLA_ABI_VERSION 3
+#define FLA_ABI_VERSION 4
 
 enum {
   FLA_OK = 0,
@@ -120,6 +120,54 @@ int fla_sm100_bwd(const FlaArgs* args);
  * calling fla_sm100_fwd / fla_sm100_bwd with s_init / r_init. The reference has no counterpart:
  * its kernels are quadratic and keep no state (flashlinear/kernels/linear_attn_kernels.py:63). */
 int fla_sm100_state(const FlaArgs* args, int which);
+
+/* ---- sequence sharding: state pass fused with the exchange between the GPUs of one node ----
+ * Every rank holds N/W consecutive tokens of every head. fla_sm100_state_exchange() computes the
+ * per-segment states of this rank's tokens (which = 0: sum k^T v, reads k, v; which = 1: sum q^T dO,
+ * reads q, d_o) and then, in ONE kernel, (1) scans them, (2) stores this rank's total straight into
+ * the inbox of every peer GPU over NVLink (plain stores to peer-mapped memory) and raises a flag
+ * there, (3) waits -- bounded -- for the peers' flags in its own inbox, (4) adds the totals of the
+ * ranks before it (after it when `reverse`) to every segment prefix. Afterwards
+ *   - args->workspace holds the per-segment prefixes including the other GPUs' contribution: call
+ *     fla_sm100_fwd / fla_sm100_product with segment_states_ready = 1 and no s_init;
+ *   - remote_out (optional) holds the other GPUs' contribution alone, inclusive_out (optional) that
+ *     plus this rank's total: the s_init / r_init / s_last of the backward call.
+ * No NCCL call is involved. The reference has no counterpart (it has no multi-GPU code).
+ *
+ * inbox[d] / flags[d] are the base addresses of rank d's inbox and flag array AS MAPPED INTO THIS
+ * PROCESS (peer-mapped device memory, e.g. opened from CUDA IPC handles); inbox[rank] / flags[rank]
+ * are this rank's own. Sizes: fla_sm100_exchange_bytes(). Both must be zero before the first use.
+ * `epoch` starts at 1 and increases by 1 with every exchange on these buffers, on all ranks alike.
+ * All ranks must make the same sequence of calls. A peer that never shows up makes the wait run
+ * out after about 0.4 s: bit 1 of *status is set and the call's results are invalid. */
+#define FLA_MAX_RANKS 8
+typedef struct FlaExchange {
+  int32_t rank, world;
+  int32_t reverse; /* 0: add the states of the ranks before this one; 1: of the ranks after it */
+  uint32_t epoch;
+  float* inbox[FLA_MAX_RANKS];
+  uint32_t* flags[FLA_MAX_RANKS];
+  float* remote_out;    /* optional, fp32 [batch*heads, dk, dv] */
+  float* inclusive_out; /* optional, fp32 [batch*heads, dk, dv] */
+} FlaExchange;
+/* Bytes of one rank's inbox (*inbox_bytes) and flag array (*flag_bytes) for these shapes. */
+int fla_sm100_exchange_bytes(const FlaArgs* args, int world, size_t* inbox_bytes, size_t* flag_bytes);
+/* Scratch needed in args->workspace by fla_sm100_state_exchange (never 0). */
+size_t fla_sm100_exchange_workspace_bytes(const FlaArgs* args);
+int fla_sm100_state_exchange(const FlaArgs* args, int which, const FlaExchange* exchange);
+/* Set-up helpers for the exchange buffers (the only calls of this library that allocate).
+ * alloc: cudaMalloc + zero fill on the current device and the 64-byte CUDA IPC handle of the
+ * allocation, to be sent to the other ranks of the node. open: maps a peer's allocation into this
+ * process WITH THE CALLER'S DEVICE CURRENT, so that this device's kernels can store into it; the
+ * mapping is verified with a runtime copy before it is returned. close / free undo them. */
+int fla_sm100_exchange_alloc(size_t bytes, void** ptr, unsigned char* handle64);
+int fla_sm100_exchange_open(const unsigned char* handle64, void** ptr);
+int fla_sm100_exchange_close(void* ptr);
+int fla_sm100_exchange_free(void* ptr);
+/* Lets kernels on the current device store into memory of `peer_device` (cudaDeviceEnablePeerAccess;
+ * already-enabled is not an error). Call once per peer before the first exchange: mapping a peer's
+ * buffer through CUDA IPC does not by itself make it writable from another device's kernels. */
+int fla_sm100_enable_peer_access(int peer_device);
 
 /* The building block of both passes: o_i = sum_{j<=i} (q_i . k_j) v_j, or with anticausal != 0 the
  * sum over j >= i (tokens walked from the last to the first; s_init / s_final then refer to the

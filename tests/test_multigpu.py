@@ -42,7 +42,12 @@ def _worker(rank, world, port, mode):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
     from flashlinear import LinearAttention
     from flashy_linear_attention_b200 import ops
-    from flashy_linear_attention_b200.sharding import SequenceShardedLinearAttention, shard_batch_heads
+    from flashy_linear_attention_b200.sharding import (
+        PeerShardedLinearAttention,
+        PeerStateExchange,
+        SequenceShardedLinearAttention,
+        shard_batch_heads,
+    )
 
     B, H, N, D = 2, 4, 2048, 128
     q, k, v, dy = _make(B, H, N, D, device)
@@ -50,11 +55,22 @@ def _worker(rank, world, port, mode):
     qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
     full = LinearAttention.apply(qf, kf, vf)
     full.backward(dy)
-    if mode == "sequence":
+    if mode in ("sequence", "sequence_peer"):
         lo, hi = rank * N // world, (rank + 1) * N // world
         ql, kl, vl = (t[:, :, lo:hi].contiguous().requires_grad_(True) for t in (q, k, v))
-        out = SequenceShardedLinearAttention.apply(ql, kl, vl, None)
-        out.backward(dy[:, :, lo:hi].contiguous())
+        if mode == "sequence":
+            out = SequenceShardedLinearAttention.apply(ql, kl, vl, None)
+            out.backward(dy[:, :, lo:hi].contiguous())
+        else:
+            # exchange fused into the state kernels over peer-mapped memory; two steps, so that both
+            # parity buffers and the epoch counters are exercised
+            ex = PeerStateExchange(B, H, D, D, device)
+            for step in range(2):
+                ql.grad = kl.grad = vl.grad = None
+                out = PeerShardedLinearAttention.apply(ql, kl, vl, ex)
+                out.backward(dy[:, :, lo:hi].contiguous())
+            torch.cuda.synchronize()
+            ex.close()
         want = (full[:, :, lo:hi], qf.grad[:, :, lo:hi], kf.grad[:, :, lo:hi], vf.grad[:, :, lo:hi])
     else:
         ql, kl, vl = (shard_batch_heads(t, rank, world).contiguous().requires_grad_(True) for t in (q, k, v))
@@ -71,7 +87,7 @@ def _worker(rank, world, port, mode):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["sequence", "batch_head"])
+@pytest.mark.parametrize("mode", ["sequence", "sequence_peer", "batch_head"])
 def test_two_gpu_sharding(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
