@@ -5,9 +5,10 @@ flashlinear/kernels/__init__.py:1-5):
     LinearAttention, LinearAttentionSmallVHD,
     linear_flash_wrapper_fwd, linear_flash_wrapper_bwd,
     linear_flash_wrapper_fwd_smallv_hd, linear_flash_wrapper_bwd_smallv_hd
-plus the lower-level causal_dot_product_fwd / causal_dot_product_bwd (running-state arguments).
+plus the lower-level causal_dot_product_fwd / causal_dot_product_bwd (running-state arguments),
+LinearAttentionResumable (state carried across calls) and host.HostPipeline (pinned host tensors).
 """
-from .functions import LinearAttention, LinearAttentionSmallVHD
+from .functions import LinearAttention, LinearAttentionResumable, LinearAttentionSmallVHD
 from .ops import (
     causal_dot_product_bwd,
     causal_dot_product_fwd,
@@ -22,6 +23,7 @@ from .ops import (
 __all__ = [
     "LinearAttention",
     "LinearAttentionSmallVHD",
+    "LinearAttentionResumable",
     "linear_flash_wrapper_fwd",
     "linear_flash_wrapper_bwd",
     "linear_flash_wrapper_fwd_smallv_hd",

@@ -78,3 +78,54 @@ class LinearAttentionSmallVHD(Function):
     def backward(ctx: Any, grad_output: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         gradq, gradk, gradv = _backward_with_state(ctx, grad_output, smallv=True)
         return gradq, gradk, gradv
+
+
+class LinearAttentionResumable(Function):
+    """Causal linear attention that carries its running state across calls.
+
+    ``out, s_final = LinearAttentionResumable.apply(q, k, v, s_init)`` where ``s_init`` /
+    ``s_final`` are fp32 ``[batch, heads, dk, dv]`` (sum of k_j^T v_j over the tokens before /
+    up to the end of this call; ``s_init=None`` starts from zero). Feeding ``s_final`` of one call
+    as ``s_init`` of the next gives what one call over the concatenated tokens gives: chunked
+    prefill, recurrent decoding, or training on a long sequence piece by piece. The state is
+    differentiable: the backward returns the gradient of ``s_init`` and accepts one for ``s_final``.
+
+    Not part of the reference, whose Functions (flashlinear/linear_attn.py:11-31) always start from
+    an empty state. Head dims up to 128.
+    """
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
+    def forward(ctx: Any, q, k, v, s_init=None):
+        ops.check_forward_preconditions(q, v, smallv=q.shape[-1] != v.shape[-1])
+        B, H, _, dk = q.shape
+        dv = v.shape[-1]
+        if s_init is not None:
+            # autocast's cast_inputs also turns the fp32 state to bf16; the state stays fp32
+            s_init = s_init.to(torch.float32).contiguous()
+            if tuple(s_init.shape) != (B, H, dk, dv):
+                raise ValueError(f"s_init must have shape {(B, H, dk, dv)}")
+        s_final = torch.empty(B, H, dk, dv, dtype=torch.float32, device=q.device)
+        out = ops.causal_dot_product_fwd(
+            q, k, v, s_init=None if s_init is None else s_init.view(B * H, dk, dv),
+            s_final=s_final.view(B * H, dk, dv))
+        ctx.save_for_backward(q, k, v, s_init, s_final)
+        return out, s_final
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx: Any, grad_output, grad_s_final):
+        q, k, v, s_init, s_final = ctx.saved_tensors
+        B, H, _, dk = q.shape
+        dv = v.shape[-1]
+        flat = (B * H, dk, dv)
+        if grad_output is None:
+            grad_output = torch.zeros_like(v)
+        r_init = None if grad_s_final is None else grad_s_final.to(torch.float32).contiguous().view(flat)
+        r_final = torch.empty(flat, dtype=torch.float32, device=q.device) if ctx.needs_input_grad[3] else None
+        s_last = s_final.view(flat) if ops.backward_uses_final_state(q, v) else None
+        dq, dk_, dv_ = ops.causal_dot_product_bwd(
+            grad_output.contiguous(), q, k, v,
+            s_init=None if s_init is None else s_init.view(flat),
+            r_init=r_init, r_final=r_final, s_last=s_last)
+        return dq, dk_, dv_, None if r_final is None else r_final.view(B, H, dk, dv)

@@ -127,3 +127,10 @@ def test_shard_batch_heads_partitions_every_head_once():
         assert torch.equal(seen.sort().values, t.reshape(-1))
     with pytest.raises(ValueError):
         shard_batch_heads(t, 0, 3)
+
+
+def test_host_pipeline_has_no_cpu_fallback():
+    from flashy_linear_attention_b200.host import HostPipeline
+
+    with pytest.raises(RuntimeError, match="CUDA"):
+        HostPipeline("cpu")

@@ -379,3 +379,75 @@ def test_full_size_properties(cfg):
     _check("dq[head]", _np(dq[b, h]), rq)
     _check("dk[head]", _np(dk[b, h]), rk)
     _check("dv[head]", _np(dv[b, h]), rv)
+
+
+@pytest.mark.parametrize("shape,heads_per_slab", [((2, 5, 512, 64, 64), 3), ((1, 4, 1024, 128, 128), 16),
+                                                  ((2, 3, 256, 96, 32), 2)],
+                         ids=["ragged-slabs", "one-slab", "smallv"])
+def test_host_pipeline_equals_oracle_and_device_path(shape, heads_per_slab):
+    """Pinned host tensors streamed in slabs of heads give what the device-resident call gives."""
+    from flashy_linear_attention_b200.host import HostPipeline
+
+    ops = _ops()
+    B, H, N, dk, dv = shape
+    rng = np.random.default_rng(7)
+    q = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, dk))).astype(np.float32))
+    k = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, dk))).astype(np.float32))
+    v = orc.bf16_round(rng.standard_normal((B, H, N, dv)).astype(np.float32))
+    dy = orc.bf16_round(rng.standard_normal((B, H, N, dv)).astype(np.float32))
+    host_in = [torch.from_numpy(a).to(torch.bfloat16).pin_memory() for a in (q, k, v, dy)]
+    host_out = [torch.full(s, float("nan"), dtype=torch.bfloat16).pin_memory()
+                for s in ((B, H, N, dv), (B, H, N, dk), (B, H, N, dk), (B, H, N, dv))]
+    pipe = HostPipeline(DEV, heads_per_slab=heads_per_slab, depth=2)
+    for _ in range(2):  # the second call reuses the staging buffers
+        pipe.fwd_bwd(*host_in, *host_out)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    q64, k64, v64, dy64 = (t.astype(np.float64) for t in (q, k, v, dy))
+    want = (orc.linear_ref(q64, k64, v64),) + tuple(orc.linear_ref_grads(q64, k64, v64, dy64))
+    for name, got, ref in zip(("out", "dq", "dk", "dv"), host_out, want):
+        assert not torch.isnan(got.float()).any(), f"{name}: rows left unwritten"
+        _check(name, got.float().numpy(), ref)
+    tq, tk, tv, tdy = (t.to(DEV) for t in host_in)
+    dev_out = ops.causal_dot_product_fwd(tq, tk, tv)
+    _check("out vs device-resident call", host_out[0].float().numpy(), _np(dev_out))
+    with pytest.raises(ValueError):
+        pipe.fwd_bwd(host_in[0].clone(), *host_in[1:], *host_out)  # not pinned
+
+
+@pytest.mark.parametrize("shape", [(2, 2, 512, 128, 128), (1, 3, 384, 64, 64), (1, 2, 256, 96, 32)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_resumable_function_carries_state_and_gradients(shape):
+    """Two calls chained through the state (and autograd through it) equal one call on all tokens."""
+    from flashy_linear_attention_b200 import LinearAttentionResumable
+
+    ops = _ops()
+    B, H, N, dk, dv = shape
+    h = N // 2 if (N // 2) % 64 == 0 else 64
+    rng = np.random.default_rng(11)
+    q = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, dk))).astype(np.float32))
+    k = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, dk))).astype(np.float32))
+    v = orc.bf16_round(rng.standard_normal((B, H, N, dv)).astype(np.float32))
+    dy = orc.bf16_round(rng.standard_normal((B, H, N, dv)).astype(np.float32))
+    tq, tk, tv, tdy = (_to_dev(t).requires_grad_(True) for t in (q, k, v, dy))
+    o1, s1 = LinearAttentionResumable.apply(tq[:, :, :h], tk[:, :, :h], tv[:, :, :h], None)
+    o2, s2 = LinearAttentionResumable.apply(tq[:, :, h:], tk[:, :, h:], tv[:, :, h:], s1)
+    out = torch.cat([o1, o2], dim=2)
+    assert s2.dtype == torch.float32 and tuple(s2.shape) == (B, H, dk, dv)
+    gq, gk, gv = torch.autograd.grad(out, (tq, tk, tv), tdy.detach())
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    q64, k64, v64, dy64 = (t.astype(np.float64) for t in (q, k, v, dy))
+    _check("out", _np(out), orc.linear_ref(q64, k64, v64))
+    rq, rk, rv = orc.linear_ref_grads(q64, k64, v64, dy64)
+    _check("dq", _np(gq), rq)
+    _check("dk", _np(gk), rk)
+    _check("dv", _np(gv), rv)
+    want_s = np.matmul(np.swapaxes(k64, -1, -2), v64)
+    assert orc.max_rel_error(_np(s2), want_s) < 1e-4
+    # a loss on the state alone: d/dk sum(s_final * W) = v W^T, d/dv = k W
+    w = torch.from_numpy(rng.standard_normal((B, H, dk, dv)).astype(np.float32)).to(DEV)
+    _, s = LinearAttentionResumable.apply(tq, tk, tv, None)
+    gk2, gv2 = torch.autograd.grad((s * w).sum(), (tk, tv))
+    _check("dk from the state", _np(gk2), np.matmul(v64, np.swapaxes(w.double().cpu().numpy(), -1, -2)))
+    _check("dv from the state", _np(gv2), np.matmul(k64, w.double().cpu().numpy()))
