@@ -11,7 +11,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libflashlinear_sm100.so")
 
-FLA_ABI_VERSION = 4
+FLA_ABI_VERSION = 5
 FLA_MAX_RANKS = 8
 
 
@@ -76,6 +76,8 @@ EXPORTED_SYMBOLS = (
     "fla_sm100_state",
     "fla_sm100_fwd_static_scratch",
     "fla_sm100_product",
+    "fla_sm100_pad_rows",
+    "fla_sm100_unpad_rows",
     "fla_sm100_exchange_bytes",
     "fla_sm100_exchange_workspace_bytes",
     "fla_sm100_state_exchange",
@@ -118,6 +120,11 @@ def load() -> ctypes.CDLL:
     lib.fla_sm100_fwd_static_scratch.argtypes = [ctypes.POINTER(FlaArgs)]
     lib.fla_sm100_product.restype = ctypes.c_int
     lib.fla_sm100_product.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_int]
+    for name in ("fla_sm100_pad_rows", "fla_sm100_unpad_rows"):
+        fn = getattr(lib, name)
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
+                       ctypes.c_void_p]
     lib.fla_sm100_exchange_bytes.restype = ctypes.c_int
     lib.fla_sm100_exchange_bytes.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_int,
                                              ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]

@@ -12,9 +12,11 @@
 // dV and dK run side by side in one grid so that their shared reads of q and dO hit in L2.
 #include "../../include/flashlinear_sm100.h"
 #include "fla_kernel.cuh"
+#include "fla_wide_kernel.cuh"
 
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
@@ -282,6 +284,83 @@ __global__ void fla_state_exchange_kernel(const ExchangeParams xp) {
   if (xp.inclusive_out) xp.inclusive_out[ext_idx] = run;
 }
 
+// ---------------------------------------------------------------- row padding
+// TMA needs 16-byte row strides, which a contiguous bf16 tensor with an odd head dim (273-dim
+// Taylor features) does not have. These two kernels copy between rows of d elements and rows of
+// dpad elements (dpad a multiple of 8); both sides contiguous.
+//
+// Both kernels give every block a run of kPadRowsPerBlock rows, so that all index arithmetic
+// inside a block is 32-bit.
+constexpr int kPadRowsPerBlock = 32;
+
+// Pad: one thread per 16-byte piece of the destination; the (up to) 8 source elements start at an
+// arbitrary 2-byte offset, so they are fetched as aligned 32-bit words and shifted.
+__global__ void fla_pad_rows_kernel(const uint32_t* __restrict__ src, uint4* __restrict__ dst,
+                                    long long rows, int d, int dpad) {
+  const int pieces = dpad >> 3;
+  for (long long blk = blockIdx.x; blk * kPadRowsPerBlock < rows; blk += gridDim.x) {
+    const long long row0 = blk * kPadRowsPerBlock;
+    const int nrows = static_cast<int>(min(static_cast<long long>(kPadRowsPerBlock), rows - row0));
+    // the block's source elements start at element row0 * d (an even number: 32 rows per block)
+    const uint32_t* bsrc = src + ((row0 * d) >> 1);
+    uint4* bdst = dst + row0 * pieces;
+    const int total = nrows * pieces;
+    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+      const int r = idx / pieces;
+      const int c0 = (idx - r * pieces) * 8;
+      const int valid = min(8, d - c0);  // <= 0: the piece is all padding
+      uint32_t w[5] = {0u, 0u, 0u, 0u, 0u};
+      uint32_t out[4] = {0u, 0u, 0u, 0u};
+      if (valid > 0) {
+        const int e0 = r * d + c0;  // first source element, relative to the block
+        const int w0 = e0 >> 1;
+        const int odd = e0 & 1;
+        const int nwords = (odd + valid + 1) >> 1;
+#pragma unroll
+        for (int j = 0; j < 5; ++j)
+          if (j < nwords) w[j] = bsrc[w0 + j];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t x = odd ? __funnelshift_r(w[j], w[j + 1], 16) : w[j];
+          const int left = valid - 2 * j;  // elements of this word that are inside the row
+          if (left <= 0) x = 0u;
+          else if (left == 1) x &= 0xFFFFu;
+          out[j] = x;
+        }
+      }
+      bdst[idx] = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+  }
+}
+
+// Unpad: one thread per 32-bit word of the destination (two elements, possibly of two rows).
+__global__ void fla_unpad_rows_kernel(const unsigned short* __restrict__ src,
+                                      unsigned short* __restrict__ dst, long long rows, int d,
+                                      int dpad) {
+  for (long long blk = blockIdx.x; blk * kPadRowsPerBlock < rows; blk += gridDim.x) {
+    const long long row0 = blk * kPadRowsPerBlock;
+    const int nrows = static_cast<int>(min(static_cast<long long>(kPadRowsPerBlock), rows - row0));
+    const unsigned short* bsrc = src + row0 * dpad;
+    unsigned short* bdst = dst + row0 * d;  // 4-byte aligned: 32 rows per block
+    const int total_elems = nrows * d;
+    const int total = (total_elems + 1) >> 1;
+    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+      const int e0 = idx * 2;
+      const int r0 = e0 / d;
+      const int c0 = e0 - r0 * d;
+      const uint32_t lo = bsrc[r0 * dpad + c0];
+      if (e0 + 1 < total_elems) {
+        const int r1 = (c0 + 1 < d) ? r0 : r0 + 1;
+        const int c1 = (c0 + 1 < d) ? c0 + 1 : 0;
+        const uint32_t hi = bsrc[r1 * dpad + c1];
+        reinterpret_cast<uint32_t*>(bdst)[idx] = lo | (hi << 16);
+      } else {
+        bdst[e0] = static_cast<unsigned short>(lo);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- launch plumbing
 struct DeviceInfo {
   int sm_count;
@@ -319,6 +398,10 @@ int device_info(DeviceInfo** out) {
       ok &= cudaFuncSetAttribute(fla::fla_chunk_kernel<128, 128>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  fla::Cfg<128, 128>::SMEM_BYTES) == cudaSuccess;
+      ok &= cudaFuncSetAttribute(fla::fla_wide_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 fla::WideCfg<2>::SMEM_BYTES) == cudaSuccess;
+      ok &= cudaFuncSetAttribute(fla::fla_wide_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 fla::WideCfg<3>::SMEM_BYTES) == cudaSuccess;
       d.attr_set[0] = d.attr_set[1] = ok;
       ready[dev].store(2, std::memory_order_release);
     } else {
@@ -538,6 +621,69 @@ int run_state(const Operand& bop, const Operand& cop, int B, int H, int N, int d
   return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
 }
 
+// Head dims above the 128-wide tiles of fla_chunk_kernel.
+constexpr int kWideMaxDim = 384;   // widest a/b (wide-a) or c/out (wide-c) head dim
+constexpr int kWideNarrowDim = 64; // widest c/out of the wide-a kernel
+
+bool is_wide_a(int da, int dc) { return da > 128 && da <= kWideMaxDim && dc <= kWideNarrowDim; }
+bool is_wide_c(int da, int dc) { return da <= 128 && dc > 128 && dc <= kWideMaxDim; }
+
+// a, b wider than 128 columns, c and out at most 64: fla_wide_kernel, one CTA per (batch, head).
+int run_wide_a(const Product& pd, int B, int H, int N, int da, int dc, int32_t* status,
+               cudaStream_t stream) {
+  if (!is_wide_a(da, dc)) return FLA_ERR_UNSUPPORTED;
+  if (pd.ext_init != nullptr || pd.ext_final != nullptr) return FLA_ERR_UNSUPPORTED;
+  int rc;
+  if ((rc = check_operand(pd.a, B, H)) || (rc = check_operand(pd.b, B, H)) ||
+      (rc = check_operand(pd.c, B, H)) || (rc = check_operand(pd.out, B, H)))
+    return rc;
+  fla::WideParams wp;
+  memset(&wp, 0, sizeof(wp));
+  if ((rc = encode_map(&wp.a, pd.a, B, H, N)) || (rc = encode_map(&wp.b, pd.b, B, H, N)) ||
+      (rc = encode_map(&wp.c, pd.c, B, H, N)) || (rc = encode_map(&wp.o, pd.out, B, H, N, 32)))
+    return rc;
+  wp.flags = pd.flags;
+  wp.n_tokens = N;
+  wp.heads = H;
+  wp.nchunks = (N + fla::kWideChunk - 1) / fla::kWideChunk;
+  wp.da = da;
+  wp.status = status;
+  const dim3 grid(1, 1, B * H);
+  if (da <= 256)
+    fla::fla_wide_kernel<2><<<grid, fla::kWideThreads, fla::WideCfg<2>::SMEM_BYTES, stream>>>(wp);
+  else
+    fla::fla_wide_kernel<3><<<grid, fla::kWideThreads, fla::WideCfg<3>::SMEM_BYTES, stream>>>(wp);
+  ++g_last_launches;
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    FLA_LOG_FAILURE("launch of fla_wide_kernel (da %d) failed: %s", da, cudaGetErrorString(e));
+  return e == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
+
+// c and out wider than 128 columns, a and b at most 128: the output columns are independent, so
+// every 128-column slice of c/out is one problem of fla_chunk_kernel<128,128>; the slices of a
+// head run side by side in one grid and share their a and b reads in L2.
+int run_wide_c(const Product& pd, int B, int H, int N, int da, int dc, int32_t* status,
+               cudaStream_t stream, const DeviceInfo& dev) {
+  if (!is_wide_c(da, dc)) return FLA_ERR_UNSUPPORTED;
+  if (pd.ext_init != nullptr || pd.ext_final != nullptr) return FLA_ERR_UNSUPPORTED;
+  // Equal slices (rounded up to 16 columns, which keeps every slice 16-byte aligned): CTAs of a
+  // narrow last slice would cost a full CTA slot for little traffic.
+  Product slices[3];
+  const int nslices = (dc + 127) / 128;
+  const int width = ((dc + nslices - 1) / nslices + 15) / 16 * 16;
+  int n = 0;
+  for (int c0 = 0; c0 < dc; c0 += width, ++n) {
+    Product& sl = slices[n];
+    sl = pd;
+    sl.c.ptr = static_cast<const char*>(pd.c.ptr) + static_cast<size_t>(c0) * 2;
+    sl.out.ptr = static_cast<const char*>(pd.out.ptr) + static_cast<size_t>(c0) * 2;
+    sl.c.dim = sl.out.dim = (dc - c0 < width) ? dc - c0 : width;
+  }
+  // check_operand wants sn >= round-up of dim; a slice's row stride covers the whole row
+  return run_products(slices, n, B, H, N, da, 128, /*segments=*/1, nullptr, 0, status, stream, dev);
+}
+
 int check_common(const FlaArgs* a, DeviceInfo** dev) {
   if (a == nullptr) return FLA_ERR_INVALID;
   // The launch checks below read the thread's last-error slot; drop whatever an earlier,
@@ -621,6 +767,7 @@ int fla_sm100_last_launch_count(void) { return g_last_launches; }
 
 int fla_sm100_auto_segments(const FlaArgs* a, int pass) {
   if (a == nullptr) return 1;
+  if (a->dk > 128 || a->dv > 128) return 1;  // the wide paths never split the sequence
   if (a->segments > 0) return a->segments;
   int sm = 148;
   int dev = 0;
@@ -655,6 +802,9 @@ int fla_sm100_fwd(const FlaArgs* a) {
   p.ext_init = a->s_init;
   p.ext_final = a->s_final;
   p.ext_trans = 0;
+  if (is_wide_a(a->dk, a->dv))
+    return run_wide_a(p, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->status,
+                      static_cast<cudaStream_t>(a->stream));
   return run_products(&p, 1, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->segments,
                       a->workspace, a->workspace_bytes, a->status,
                       static_cast<cudaStream_t>(a->stream), *dev, a->segment_states_ready != 0);
@@ -697,6 +847,16 @@ int fla_sm100_bwd(const FlaArgs* a) {
   pk.ext_final = nullptr;
   pk.ext_trans = 1;
 
+  if (is_wide_a(a->dk, a->dv)) {
+    // SmallVHD shapes: dQ and dK have the wide head dim on the output side, dV on the a/b side.
+    if (a->s_init || a->r_init || a->r_final || a->s_last) return FLA_ERR_UNSUPPORTED;
+    if ((rc = run_wide_c(pq, a->batch, a->heads, a->seqlen, a->dv, a->dk, a->status, stream, *dev)))
+      return rc;
+    if ((rc = run_wide_c(pk, a->batch, a->heads, a->seqlen, a->dv, a->dk, a->status, stream, *dev)))
+      return rc;
+    rc = run_wide_a(pv, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->status, stream);
+    return rc;
+  }
   const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
   int nseg = a->segments > 0 ? a->segments
                              : auto_segments(3, a->batch * a->heads, nchunks, dev->sm_count);
@@ -778,6 +938,35 @@ int fla_sm100_fwd_static_scratch(const FlaArgs* a) {
                       *dev);
 }
 
+int fla_sm100_pad_rows(const void* src, void* dst, long long rows, int d, int dpad, void* stream) {
+  (void)cudaGetLastError();
+  g_last_launches = 0;
+  if (src == nullptr || dst == nullptr || rows <= 0 || d <= 0 || dpad < d) return FLA_ERR_INVALID;
+  if (dpad % 8 != 0 || reinterpret_cast<uintptr_t>(dst) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(src) % 4 != 0)
+    return FLA_ERR_ALIGNMENT;
+  const int blocks = static_cast<int>(
+      std::min<long long>((rows + kPadRowsPerBlock - 1) / kPadRowsPerBlock, 148 * 32));
+  fla_pad_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(src), static_cast<uint4*>(dst), rows, d, dpad);
+  ++g_last_launches;
+  return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
+
+int fla_sm100_unpad_rows(const void* src, void* dst, long long rows, int d, int dpad, void* stream) {
+  (void)cudaGetLastError();
+  g_last_launches = 0;
+  if (src == nullptr || dst == nullptr || rows <= 0 || d <= 0 || dpad < d) return FLA_ERR_INVALID;
+  if (reinterpret_cast<uintptr_t>(dst) % 4 != 0 || reinterpret_cast<uintptr_t>(src) % 2 != 0)
+    return FLA_ERR_ALIGNMENT;
+  const int blocks = static_cast<int>(
+      std::min<long long>((rows + kPadRowsPerBlock - 1) / kPadRowsPerBlock, 148 * 32));
+  fla_unpad_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned short*>(src), static_cast<unsigned short*>(dst), rows, d, dpad);
+  ++g_last_launches;
+  return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
+
 int fla_sm100_product(const FlaArgs* a, int anticausal) {
   DeviceInfo* dev = nullptr;
   g_last_launches = 0;
@@ -792,6 +981,12 @@ int fla_sm100_product(const FlaArgs* a, int anticausal) {
   p.ext_init = a->s_init;
   p.ext_final = a->s_final;
   p.ext_trans = 0;
+  if (is_wide_a(a->dk, a->dv))
+    return run_wide_a(p, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->status,
+                      static_cast<cudaStream_t>(a->stream));
+  if (is_wide_c(a->dk, a->dv))
+    return run_wide_c(p, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->status,
+                      static_cast<cudaStream_t>(a->stream), *dev);
   return run_products(&p, 1, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->segments,
                       a->workspace, a->workspace_bytes, a->status,
                       static_cast<cudaStream_t>(a->stream), *dev);

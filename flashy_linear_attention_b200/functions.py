@@ -27,6 +27,15 @@ def _forward_with_state(ctx: Any, q, k, v, smallv: bool):
     use it, also keeps the final state S = sum k^T v (fp32, batch*heads x dk x dv), which lets the
     backward read q, k, v, dO from HBM once instead of twice."""
     want_state = any(ctx.needs_input_grad[:3]) and q.is_cuda and ops.backward_uses_final_state(q, v)
+    ctx.keep_padded = False
+    if smallv and q.is_cuda and q.shape[-1] % 8 != 0 and any(ctx.needs_input_grad[:3]):
+        # Head dims such as 273 have rows the kernels cannot address in place. Repack q and k once,
+        # keep the repacked views for the backward, and let the backward return dQ and dK as views
+        # of row-padded tensors (same values and shape as the reference's gradients, which are
+        # contiguous, linear_attn_kernels_smallv_hd.py:384-386; one copy pass per tensor less).
+        ops.check_forward_preconditions(q, v, smallv)
+        q, k = ops.kernel_view(q), ops.kernel_view(k)
+        ctx.keep_padded = True
     if not want_state:
         out = linear_flash_wrapper_fwd_smallv_hd(q, k, v) if smallv else linear_flash_wrapper_fwd(q, k, v)
         ctx.save_for_backward(q, k, v)
@@ -44,6 +53,8 @@ def _forward_with_state(ctx: Any, q, k, v, smallv: bool):
 def _backward_with_state(ctx: Any, grad_output, smallv: bool):
     if not ctx.has_state:
         query, key, value = ctx.saved_tensors
+        if ctx.keep_padded:
+            return ops.causal_dot_product_bwd(grad_output, query, key, value, keep_padded=True)
         fn = linear_flash_wrapper_bwd_smallv_hd if smallv else linear_flash_wrapper_bwd
         return fn(grad_output, query, key, value)
     query, key, value, s_final = ctx.saved_tensors

@@ -17,7 +17,9 @@ import torch
 from . import _lib
 from ._lib import FlaArgs, FlaTensor
 
-KERNEL_HEAD_DIM = 128  # widest head-dim tile of the kernels; wider dims are assembled from slices
+KERNEL_HEAD_DIM = 128  # widest head-dim tile of the main kernel
+WIDE_HEAD_DIM = 384    # widest q/k head dim of the wide (SmallVHD) kernel ...
+WIDE_NARROW_DIM = 64   # ... which takes v head dims up to this; other shapes are assembled from slices
 MAX_HEAD_DIM = 256     # cap of LinearAttention, as in the reference (linear_attn_kernels.py:322)
 MAX_HEAD_DIM_QK_SMALLV = 512  # cap of q/k for LinearAttentionSmallVHD (273-dim Taylor features fit)
 
@@ -68,42 +70,81 @@ def _check_inputs(*tensors: torch.Tensor) -> None:
             raise ValueError("flashlinear: expected [batch, heads, seq, head_dim] tensors")
 
 
-def _kernel_view(t: torch.Tensor) -> torch.Tensor:
-    """Returns `t` if the kernels can read it in place (unit innermost stride, 16-byte aligned
-    base and row/head/batch strides), else a repacked copy whose rows are padded to 8 elements."""
+def _addressable(t: torch.Tensor) -> bool:
+    """True if the kernels can read or write `t` in place: unit innermost stride, 16-byte aligned
+    base and row/head/batch strides (what a TMA tensor map needs)."""
     d = t.shape[-1]
     ok = t.stride(3) == 1 and t.data_ptr() % 16 == 0 and t.stride(2) >= d
     for dim in (0, 1, 2):
         if t.shape[dim] > 1 and t.stride(dim) % 8 != 0:
             ok = False
-    if ok:
-        return t
+    return ok
+
+
+def _padded_empty(shape, dtype, device) -> torch.Tensor:
+    """View [..., :d] of a fresh tensor whose rows are padded to a multiple of 8 elements."""
+    d = shape[-1]
     dpad = (d + 7) // 8 * 8
-    buf = torch.empty(t.shape[:-1] + (dpad,), dtype=t.dtype, device=t.device)
-    view = buf[..., :d]
-    view.copy_(t)
+    buf = torch.empty(tuple(shape[:-1]) + (dpad,), dtype=dtype, device=device)
+    return buf[..., :d]
+
+
+def _rows_call(name: str, src: torch.Tensor, dst: torch.Tensor, rows: int, d: int, dpad: int) -> None:
+    lib = _lib.load()
+    with torch.cuda.device(src.device):
+        rc = getattr(lib, name)(src.data_ptr(), dst.data_ptr(), rows, d, dpad,
+                                torch.cuda.current_stream(src.device).cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"flashlinear: {name} returned {rc}: {_lib.strerror(rc)}")
+
+
+def _kernel_view(t: torch.Tensor) -> torch.Tensor:
+    """Returns `t` if the kernels can read it in place, else a repacked copy whose rows are padded
+    to 8 elements (the library's pad kernel for contiguous tensors, a strided torch copy otherwise)."""
+    if _addressable(t):
+        return t
+    view = _padded_empty(t.shape, t.dtype, t.device)
+    d = t.shape[-1]
+    if t.is_contiguous() and t.data_ptr() % 4 == 0:
+        _rows_call("fla_sm100_pad_rows", t, view, t.numel() // d, d, view.stride(2))
+    else:
+        view.copy_(t)
     return view
 
 
-def _out_like(t: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+def kernel_view(t: torch.Tensor) -> torch.Tensor:
+    """Public form of the repack: callers that run several passes over the same tensor (forward then
+    backward) repack it once and hand the view to every pass."""
+    return _kernel_view(t)
+
+
+def _out_like(t: torch.Tensor, keep_padded: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """Output with the layout of ``torch.empty_like(t)`` plus the view the kernel writes to
-    (a padded scratch tensor when empty_like's layout is not addressable by the kernels)."""
+    (a padded scratch tensor when empty_like's layout is not addressable by the kernels).
+    keep_padded=True returns the padded view as the output itself (no copy back)."""
+    if keep_padded and t.shape[-1] % 8 != 0:
+        view = _padded_empty(t.shape, t.dtype, t.device)
+        return view, view
     out = torch.empty_like(t)
     kv = _kernel_view_for_output(out)
     return out, kv
 
 
 def _kernel_view_for_output(out: torch.Tensor) -> torch.Tensor:
-    d = out.shape[-1]
-    ok = out.stride(3) == 1 and out.data_ptr() % 16 == 0 and out.stride(2) >= d
-    for dim in (0, 1, 2):
-        if out.shape[dim] > 1 and out.stride(dim) % 8 != 0:
-            ok = False
-    if ok:
+    if _addressable(out):
         return out
-    dpad = (d + 7) // 8 * 8
-    buf = torch.empty(out.shape[:-1] + (dpad,), dtype=out.dtype, device=out.device)
-    return buf[..., :d]
+    return _padded_empty(out.shape, out.dtype, out.device)
+
+
+def _copy_back(full: torch.Tensor, view: torch.Tensor) -> None:
+    """Result from the padded scratch rows into the caller-layout output."""
+    if view is full:
+        return
+    d = full.shape[-1]
+    if full.is_contiguous() and full.data_ptr() % 4 == 0:
+        _rows_call("fla_sm100_unpad_rows", view, full, full.numel() // d, d, view.stride(2))
+    else:
+        full.copy_(view)
 
 
 def _desc(t: Optional[torch.Tensor]) -> FlaTensor:
@@ -163,6 +204,13 @@ def _product_call(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, out: torch.
     _call(3, args, a.device, which=1 if anticausal else 0)
 
 
+def _native_dims(da: int, dc: int) -> bool:
+    """Head-dim pairs (a/b side, c/out side) that one library call covers."""
+    return (da <= KERNEL_HEAD_DIM and dc <= KERNEL_HEAD_DIM) or \
+           (KERNEL_HEAD_DIM < da <= WIDE_HEAD_DIM and dc <= WIDE_NARROW_DIM) or \
+           (da <= KERNEL_HEAD_DIM and KERNEL_HEAD_DIM < dc <= WIDE_HEAD_DIM)
+
+
 def _product_sliced(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, like: torch.Tensor, anticausal: bool) -> torch.Tensor:
     """Causal product for head dims above the kernels' 128-wide tiles, by linearity: output columns
     are independent (slices of c), and (a_i . b_j) is the sum over slices of the a/b head dim, so
@@ -171,6 +219,10 @@ def _product_sliced(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, like: tor
     da, dc = a.shape[-1], c.shape[-1]
     W = KERNEL_HEAD_DIM
     out, ov = _out_like(like)
+    if _native_dims(da, dc):
+        _product_call(av, bv, cv, ov, anticausal)
+        _copy_back(out, ov)
+        return out
     for c0 in range(0, dc, W):
         c1 = min(dc, c0 + W)
         if da <= W:
@@ -183,8 +235,7 @@ def _product_sliced(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, like: tor
             _product_call(av[..., a0:a1], bv[..., a0:a1], cv[..., c0:c1], part, anticausal)
             acc = part.float() if acc is None else acc + part.float()
         ov[..., c0:c1] = acc.to(c.dtype)
-    if ov is not out:
-        out.copy_(ov)
+    _copy_back(out, ov)
     return out
 
 
@@ -211,7 +262,7 @@ def causal_dot_product_fwd(
     if dk > KERNEL_HEAD_DIM or dv > KERNEL_HEAD_DIM:
         if s_init is not None or s_final is not None:
             raise NotImplementedError("running-state arguments need head dims <= 128")
-        return _product_sliced(q, k, v, v, anticausal=False)
+        return _product_sliced(q, k, v, v, anticausal=False)  # one library call for SmallVHD shapes
     qv, kv_, vv = _kernel_view(q), _kernel_view(k), _kernel_view(v)
     out, ov = _out_like(v)
     a = FlaArgs()
@@ -225,8 +276,7 @@ def causal_dot_product_fwd(
             raise ValueError("flashlinear: s_final cannot be combined with segment_workspace")
         a.segment_states_ready = 1
     _call(0, a, q.device, workspace=segment_workspace)
-    if ov is not out:
-        out.copy_(ov)
+    _copy_back(out, ov)
     return out
 
 
@@ -240,15 +290,21 @@ def causal_dot_product_bwd(
     r_final: Optional[torch.Tensor] = None,
     segments: int = 0,
     s_last: Optional[torch.Tensor] = None,
+    keep_padded: bool = False,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Gradients (dQ, dK, dV) of causal_dot_product_fwd for upstream gradient `grad_output`.
 
     s_last (optional) is the forward state after these tokens, i.e. what the forward call wrote to
-    `s_final`; with it the backward reads q, k, v, dO from HBM only once."""
+    `s_final`; with it the backward reads q, k, v, dO from HBM only once.
+    keep_padded=True: gradients whose head dim is not a multiple of 8 are returned as views of the
+    row-padded tensors the kernels wrote, instead of being copied to the contiguous layout."""
     _check_inputs(grad_output, q, k, v)
     B, H, N, dk = q.shape
     dv = v.shape[-1]
-    if dk > KERNEL_HEAD_DIM or dv > KERNEL_HEAD_DIM:
+    wide = KERNEL_HEAD_DIM < dk <= WIDE_HEAD_DIM and dv <= WIDE_NARROW_DIM
+    if wide and any(t is not None for t in (s_init, r_init, r_final, s_last)):
+        raise NotImplementedError("running-state arguments need head dims <= 128")
+    if (dk > KERNEL_HEAD_DIM or dv > KERNEL_HEAD_DIM) and not wide:
         if any(t is not None for t in (s_init, r_init, r_final, s_last)):
             raise NotImplementedError("running-state arguments need head dims <= 128")
         # the three gradients as products with permuted operands (see fla_sm100_product)
@@ -257,9 +313,9 @@ def causal_dot_product_bwd(
         dK = _product_sliced(v, grad_output, q, k, anticausal=True)
         return dQ, dK, dV
     gv, qv, kv_, vv = (_kernel_view(t) for t in (grad_output, q, k, v))
-    dQ, dQv = _out_like(q)
-    dK, dKv = _out_like(k)
-    dV, dVv = _out_like(v)
+    dQ, dQv = _out_like(q, keep_padded)
+    dK, dKv = _out_like(k, keep_padded)
+    dV, dVv = _out_like(v, keep_padded)
     a = FlaArgs()
     a.batch, a.heads, a.seqlen, a.dk, a.dv = B, H, N, dk, dv
     a.q, a.k, a.v, a.d_o = _desc(qv), _desc(kv_), _desc(vv), _desc(gv)
@@ -271,8 +327,7 @@ def causal_dot_product_bwd(
     a.segments = segments
     _call(1, a, q.device)
     for full, view in ((dQ, dQv), (dK, dKv), (dV, dVv)):
-        if view is not full:
-            full.copy_(view)
+        _copy_back(full, view)
     return dQ, dK, dV
 
 

@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define FLA_ABI_VERSION 4
+#define FLA_ABI_VERSION 5
 
 enum {
   FLA_OK = 0,
@@ -177,6 +177,20 @@ int fla_sm100_enable_peer_access(int peer_device);
  * The Python layer uses it to assemble head dims above 128 from 128-wide slices. Workspace: as for
  * pass 0. */
 int fla_sm100_product(const FlaArgs* args, int anticausal);
+
+/* Head dims above 128 (the SmallVHD shapes of flashlinear/kernels/linear_attn_kernels_smallv_hd.py:
+ * q, k wide, v narrow): fla_sm100_fwd, fla_sm100_bwd and fla_sm100_product also accept
+ *   dk in (128, 384] with dv <= 64   q/k tiles streamed in 128-column pieces by a dedicated kernel,
+ *   dk <= 128 with dv in (128, 384]  (fla_sm100_product only) output columns computed in 128-wide slices,
+ * without running-state arguments, segments or workspace. Row strides must still be multiples of
+ * 16 bytes; a contiguous tensor with an odd head dim (273) is first copied to padded rows: */
+/* dst[r][0..dpad) = src[r][0..d) followed by zeros; src and dst contiguous bf16, dpad a multiple of 8.
+ * The reference pads in registers instead (boundary_check / padding_option="zero",
+ * linear_attn_kernels_smallv_hd.py:60-75). */
+int fla_sm100_pad_rows(const void* src, void* dst, long long rows, int d, int dpad, void* stream);
+/* dst[r][0..d) = src[r][0..d) for src rows of dpad elements: the inverse copy, for gradients that
+ * must come back in the contiguous layout of torch.empty_like (linear_attn_kernels_smallv_hd.py:384). */
+int fla_sm100_unpad_rows(const void* src, void* dst, long long rows, int d, int dpad, void* stream);
 
 /* Forward pass for callers that cannot obtain device memory themselves.
  * It has no counterpart in the reference (whose wrappers allocate through torch).

@@ -138,12 +138,15 @@ def test_seeded_inputs_against_oracle(shape):
     _run_and_check(q, k, v, dy)
 
 
-@pytest.mark.parametrize("shape", [(1, 2, 256, 256, 256), (1, 2, 192, 200, 136), (2, 2, 256, 273, 64)],
+@pytest.mark.parametrize("shape", [(1, 2, 256, 256, 256), (1, 2, 192, 200, 136), (2, 2, 256, 273, 64),
+                                   (1, 1, 128, 384, 64), (1, 2, 640, 273, 32), (2, 1, 320, 144, 16),
+                                   (1, 2, 1152, 256, 64), (1, 1, 448, 330, 64)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_head_dims_above_the_kernel_tile(shape):
     """Head dims above 128 (the reference allows up to 256, flashlinear/kernels/
-    linear_attn_kernels.py:322; benchmark configuration 4 uses 273 Taylor features) are assembled
-    from 128-wide slices; same tolerance."""
+    linear_attn_kernels.py:322; benchmark configuration 4 uses 273 Taylor features): q/k up to 384
+    wide with v up to 64 run in the wide kernel (forward, dV) and as 128-column output slices
+    (dQ, dK); other shapes are assembled from 128-wide slices. Same tolerance."""
     B, H, N, dk, dv = shape
     rng = np.random.default_rng(dk * 1000 + dv)
     # scaled so that the scores stay O(1) at these widths
@@ -175,6 +178,54 @@ def test_taylor_feature_configuration_through_the_function():
     _check("dq", _np(tq.grad), rq)
     _check("dk", _np(tk.grad), rk)
     _check("dv", _np(tv.grad), rv)
+
+
+@pytest.mark.parametrize("rows,d", [(1000, 273), (77, 17), (5, 1), (4096, 83), (33, 9), (64, 271)],
+                         ids=lambda x: str(x))
+def test_row_padding_kernels_are_bit_exact(rows, d):
+    """fla_sm100_pad_rows / fla_sm100_unpad_rows: byte-for-byte copies, zero padding, round trip."""
+    ops = _ops()
+    t = torch.randn(rows, d, device=DEV).to(torch.bfloat16).reshape(1, 1, rows, d)
+    v = ops.kernel_view(t)
+    dpad = v.stride(2)
+    assert dpad % 8 == 0 and dpad >= d and v.data_ptr() % 16 == 0
+    whole = v.as_strided((rows, dpad), (dpad, 1))
+    back = torch.full_like(t, float("nan"))
+    ops._copy_back(back, v)
+    torch.cuda.synchronize()
+    assert torch.equal(whole[:, :d].view(torch.int16), t.view(rows, d).view(torch.int16))
+    assert bool((whole[:, d:].view(torch.int16) == 0).all())
+    assert torch.equal(back.view(torch.int16), t.view(torch.int16))
+
+
+def test_smallv_function_returns_reference_values_for_unaligned_head_dim():
+    """dk = 273: the Function repacks q and k once and returns dQ, dK as views of padded rows; the
+    wrappers return contiguous gradients like the reference's. Both carry the same values."""
+    from flashlinear import LinearAttentionSmallVHD
+    from flashlinear.kernels import linear_flash_wrapper_bwd_smallv_hd, linear_flash_wrapper_fwd_smallv_hd
+
+    ops = _ops()
+    torch.manual_seed(3)
+    B, H, N, dk, dv = 2, 2, 256, 273, 64
+    q = (torch.nn.functional.softplus(torch.randn(B, H, N, dk, device=DEV)) / dk ** 0.5).to(torch.bfloat16)
+    k = torch.nn.functional.softplus(torch.randn(B, H, N, dk, device=DEV)).to(torch.bfloat16)
+    v = torch.randn(B, H, N, dv, device=DEV).to(torch.bfloat16)
+    dy = torch.randn(B, H, N, dv, device=DEV).to(torch.bfloat16)
+    out_w = linear_flash_wrapper_fwd_smallv_hd(q, k, v)
+    gq_w, gk_w, gv_w = linear_flash_wrapper_bwd_smallv_hd(dy, q, k, v)
+    assert gq_w.is_contiguous() and gk_w.is_contiguous() and out_w.is_contiguous()
+    q_, k_, v_ = (t.clone().requires_grad_(True) for t in (q, k, v))
+    out_f = LinearAttentionSmallVHD.apply(q_, k_, v_)
+    gq_f, gk_f, gv_f = torch.autograd.grad(out_f, (q_, k_, v_), dy)
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    assert gq_f.shape == q.shape and gk_f.shape == k.shape
+    for a, b in ((out_w, out_f), (gq_w, gq_f), (gk_w, gk_f), (gv_w, gv_f)):
+        assert torch.equal(a, b)
+    q_.grad = None
+    out_f2 = LinearAttentionSmallVHD.apply(q_, k_, v_)
+    out_f2.backward(dy)  # accumulation into .grad accepts the padded-row views
+    assert torch.equal(q_.grad, gq_w) and torch.equal(k_.grad, gk_w)
 
 
 @pytest.mark.parametrize("segments", [2, 3, 8])
