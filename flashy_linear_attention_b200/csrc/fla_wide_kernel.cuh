@@ -14,7 +14,8 @@
 //
 // CTA layout (448 threads, one CTA per (batch, head)):
 //   warp 0       TMA producer: c tile of the chunk (own double buffer), then the a/b tile pairs
-//                into a ring of four 32 KB slots
+//                into a ring of eight 16 KB slots (one 64-column group each; a tile takes the one
+//                or two groups that hold valid columns, so padding costs no ring space)
 //   warp 1       MMA issuer (one elected lane) and TMEM owner
 //   warps 2-9    converters: P fp32 -> mask -> bf16 (TMEM), S fp32 -> bf16 (shared memory)
 //   warps 10-13  epilogue: O fp32 -> bf16 -> staging -> TMA store (each warp its own 32 rows)
@@ -42,15 +43,16 @@ struct WideParams {
 constexpr int kWideThreads = 448;
 constexpr int kWideChunk = 128;
 constexpr int kWideGroupBytes = kWideChunk * 128;   // 64 columns x 128 rows
-constexpr int kWideTileBytes = 2 * kWideGroupBytes; // 128 columns x 128 rows
-constexpr int kWideSlots = 4;
+constexpr int kWideSlots = 8;  // ring slots of one 64-column group (16 KB) each
 
 template <int NT>
 struct WideCfg {
   static_assert(NT >= 2 && NT <= 3, "state of 128*NT x 64 must fit tensor memory next to P and O");
-  static constexpr int RING_BYTES = kWideSlots * kWideTileBytes;
+  static constexpr int RING_BYTES = kWideSlots * kWideGroupBytes;
   static constexpr int C_BYTES = 2 * kWideGroupBytes;
   static constexpr int SB_BYTES = NT * 128 * 128;  // bf16 state, one 128-byte row per state row
+  // one more group after the ring: the state update of a one-group tile in the last slot reads
+  // 128 rows and so runs into the following 16 KB (the c buffers), which must exist
   static constexpr int OST_BYTES = kWideGroupBytes;
   static constexpr int BAR_BYTES = 512;
   static constexpr int SMEM_BYTES = 1024 + RING_BYTES + C_BYTES + SB_BYTES + OST_BYTES + BAR_BYTES;
@@ -142,9 +144,21 @@ fla_wide_kernel(const __grid_constant__ WideParams p) {
     return __all_sync(0xffffffffu, ok) != 0;
   };
   auto mem_chunk = [&](int i) { return descending ? (p.nchunks - 1 - i) : i; };
-  // Ring tiles are numbered in load order: chunk i, pair t holds tiles 2 * (i * NT + t) + {0: a, 1: b}.
-  auto slot_addr = [&](int tile) {
-    return smem_base + static_cast<uint32_t>(tile % kWideSlots) * kWideTileBytes;
+  // The ring is counted in 64-column groups, in load order: per chunk a_0, b_0, a_1, b_1, ...,
+  // each tile taking pair_groups(t) consecutive slots. Every pair takes an even number of groups
+  // and only the last pair can have one-group tiles, so a two-group tile always starts on an even
+  // slot: its groups are adjacent in memory and never straddle the end of the ring.
+  auto pair_groups = [&](int t) { return pair_cols(t) > 64 ? 2 : 1; };
+  int groups_per_chunk = 0;
+  for (int t = 0; t < NT; ++t) groups_per_chunk += 2 * pair_groups(t);
+  // index of the first group of tile (chunk i, pair t, w = 0: a, 1: b)
+  auto tile_group = [&](int i, int t, int w) {
+    int g = i * groups_per_chunk;
+    for (int tt = 0; tt < t; ++tt) g += 2 * pair_groups(tt);
+    return g + w * pair_groups(t);
+  };
+  auto group_addr = [&](int g) {
+    return smem_base + static_cast<uint32_t>(g % kWideSlots) * kWideGroupBytes;
   };
 
   if (warp == 0) {
@@ -160,17 +174,19 @@ fla_wide_kernel(const __grid_constant__ WideParams p) {
         ptx::tma_load_4d(c_addr + cs * kWideGroupBytes, &p.c, cfull_bar(cs), 0, tok, h, b);
       }
       for (int t = 0; t < NT; ++t) {
-        const int groups = pair_cols(t) > 64 ? 2 : 1;  // a group that is all padding is not loaded
+        const int groups = pair_groups(t);  // a group that is all padding is not loaded
         for (int w = 0; w < 2; ++w) {
-          const int tile = 2 * (i * NT + t) + w;
-          const int s = tile % kWideSlots;
-          if (!wait_uniform(empty_bar(s), ((tile / kWideSlots) & 1) ^ 1u)) { ok = false; break; }
-          if (leader) {
-            ptx::mbar_expect_tx(full_bar(s), groups * kWideGroupBytes);
-            for (int gg = 0; gg < groups; ++gg)
-              ptx::tma_load_4d(slot_addr(tile) + gg * kWideGroupBytes, w == 0 ? &p.a : &p.b,
-                               full_bar(s), t * 128 + gg * 64, tok, h, b);
+          for (int gg = 0; gg < groups; ++gg) {
+            const int g = tile_group(i, t, w) + gg;
+            const int s = g % kWideSlots;
+            if (!wait_uniform(empty_bar(s), ((g / kWideSlots) & 1) ^ 1u)) { ok = false; break; }
+            if (leader) {
+              ptx::mbar_expect_tx(full_bar(s), kWideGroupBytes);
+              ptx::tma_load_4d(group_addr(g), w == 0 ? &p.a : &p.b, full_bar(s), t * 128 + gg * 64,
+                               tok, h, b);
+            }
           }
+          if (!ok) break;
         }
         if (!ok) break;
       }
@@ -201,18 +217,19 @@ fla_wide_kernel(const __grid_constant__ WideParams p) {
         if (!wait_uniform(sb_ready, (i - 1) & 1)) break;
       }
       for (int t = 0; t < NT; ++t) {
-        const int tile_a = 2 * (i * NT + t);
-        const int tile_b = tile_a + 1;
-        if (!wait_uniform(full_bar(tile_a % kWideSlots), (tile_a / kWideSlots) & 1) ||
-            !wait_uniform(full_bar(tile_b % kWideSlots), (tile_b / kWideSlots) & 1)) {
-          ok = false;
-          break;
+        const int groups = pair_groups(t);
+        const int ga = tile_group(i, t, 0);
+        const int gb = tile_group(i, t, 1);
+        for (int gg = 0; ok && gg < groups; ++gg) {
+          ok = wait_uniform(full_bar((ga + gg) % kWideSlots), ((ga + gg) / kWideSlots) & 1) &&
+               wait_uniform(full_bar((gb + gg) % kWideSlots), ((gb + gg) / kWideSlots) & 1);
         }
+        if (!ok) break;
         ptx::tc_fence_after();
         const int ksteps = (pair_cols(t) + 15) >> 4;
-        const uint32_t a_lo = ptx::desc_lo(slot_addr(tile_a), 16);                // K-major
-        const uint32_t b_lo = ptx::desc_lo(slot_addr(tile_b), 16);                // K-major
-        const uint32_t bt_lo = ptx::desc_lo(slot_addr(tile_b), kWideGroupBytes);  // MN-major
+        const uint32_t a_lo = ptx::desc_lo(group_addr(ga), 16);                // K-major
+        const uint32_t b_lo = ptx::desc_lo(group_addr(gb), 16);                // K-major
+        const uint32_t bt_lo = ptx::desc_lo(group_addr(gb), kWideGroupBytes);  // MN-major
         if (leader) {
           for (int kk = 0; kk < ksteps; ++kk) {
             const uint32_t off = ((kk >> 2) * kWideGroupBytes + (kk & 3) * 32) >> 4;
@@ -233,8 +250,10 @@ fla_wide_kernel(const __grid_constant__ WideParams p) {
             ptx::mma_ss(tS + t * 64, bt_lo + kk * (2048 >> 4), c_lo + kk * (2048 >> 4), ptx::kDescHi,
                         IDESC_S, (have_state || kk > 0) ? 1u : 0u);
           }
-          ptx::tc_commit(empty_bar(tile_a % kWideSlots));
-          ptx::tc_commit(empty_bar(tile_b % kWideSlots));
+          for (int gg = 0; gg < groups; ++gg) {
+            ptx::tc_commit(empty_bar((ga + gg) % kWideSlots));
+            ptx::tc_commit(empty_bar((gb + gg) % kWideSlots));
+          }
         }
         __syncwarp();
       }
