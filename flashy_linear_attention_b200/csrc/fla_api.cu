@@ -210,35 +210,42 @@ __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+__device__ __forceinline__ void st_relaxed_sys(unsigned* p, unsigned v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Every thread handles the elements e0, e0 + stride, ... of one head (stride = threads of the
+// head's blocks), so that a few hundred blocks cover the state and each pays the system-scope
+// fence and the flag round trip once.
 __global__ void fla_state_exchange_kernel(const ExchangeParams xp) {
   const int bh = blockIdx.y;
   const int elems = xp.rows * xp.cols;
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
-  const bool active = e < elems;
+  const int e0 = blockIdx.x * blockDim.x + threadIdx.x;
+  const int stride = gridDim.x * blockDim.x;
   const unsigned parity = xp.epoch & 1u;
   const size_t nblocks = static_cast<size_t>(gridDim.x) * gridDim.y;
   const size_t block_id = static_cast<size_t>(bh) * gridDim.x + blockIdx.x;
   const size_t state_elems = static_cast<size_t>(xp.bh_count) * elems;
-  float* base = xp.ws + static_cast<size_t>(bh) * xp.nseg * elems + e;
+  float* head_ws = xp.ws + static_cast<size_t>(bh) * xp.nseg * elems;
 
-  // 1. this rank's total over its segments
-  float total = 0.f;
-  if (active) {
-    for (int g = 0; g < xp.nseg; ++g) total += __ldcg(base + static_cast<size_t>(g) * elems);
-  }
-  // 2. publish it: one store per peer into that peer's inbox slot for this rank
-  if (active) {
+  // 1. this rank's total over its segments, 2. published with one store per peer into that peer's
+  //    inbox slot for this rank
+  for (int e = e0; e < elems; e += stride) {
+    float total = 0.f;
+    for (int g = 0; g < xp.nseg; ++g) total += __ldcg(head_ws + static_cast<size_t>(g) * elems + e);
     const size_t slot = (static_cast<size_t>(parity) * xp.world + xp.rank) * state_elems +
                         static_cast<size_t>(bh) * elems + e;
     for (int d = 0; d < xp.world; ++d)
       if (d != xp.rank) xp.inbox[d][slot] = total;
   }
+  // Every thread orders its stores before anything it (or, through the barrier, thread d) writes
+  // afterwards, at system scope; then thread d raises this block's flag in peer d's inbox. One
+  // fence per thread and the flag stores of all peers in flight together.
   __threadfence_system();
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (static_cast<int>(threadIdx.x) < xp.world && static_cast<int>(threadIdx.x) != xp.rank) {
     const size_t f = (static_cast<size_t>(parity) * xp.world + xp.rank) * nblocks + block_id;
-    for (int d = 0; d < xp.world; ++d)
-      if (d != xp.rank) st_release_sys(xp.flags[d] + f, xp.epoch);
+    st_relaxed_sys(xp.flags[threadIdx.x] + f, xp.epoch);
   }
   // 3. wait (bounded) for the same block of every other rank. Waiting for all of them, not only the
   //    ones whose totals are needed, keeps any rank from running two exchanges ahead of another,
@@ -246,7 +253,7 @@ __global__ void fla_state_exchange_kernel(const ExchangeParams xp) {
   __shared__ int timed_out;
   if (threadIdx.x == 0) timed_out = 0;
   __syncthreads();
-  if (threadIdx.x < xp.world && static_cast<int>(threadIdx.x) != xp.rank) {
+  if (static_cast<int>(threadIdx.x) < xp.world && static_cast<int>(threadIdx.x) != xp.rank) {
     const unsigned* f = xp.flags[xp.rank] +
                         (static_cast<size_t>(parity) * xp.world + threadIdx.x) * nblocks + block_id;
     const long long t0 = clock64();
@@ -262,26 +269,27 @@ __global__ void fla_state_exchange_kernel(const ExchangeParams xp) {
     if (threadIdx.x == 0 && xp.status != nullptr) atomicOr(xp.status, 2);
     return;
   }
-  if (!active) return;
-  // 4. totals of the ranks before (after) this one, from this GPU's own inbox
-  float remote = 0.f;
   const int lo = xp.reverse ? xp.rank + 1 : 0;
   const int hi = xp.reverse ? xp.world : xp.rank;
-  for (int s = lo; s < hi; ++s)
-    remote += __ldcg(xp.inbox[xp.rank] + (static_cast<size_t>(parity) * xp.world + s) * state_elems +
-                     static_cast<size_t>(bh) * elems + e);
-  // 5. segment prefixes on top of it
-  float run = remote;
-  for (int g = 0; g < xp.nseg; ++g) {
-    float* p = base + static_cast<size_t>(g) * elems;
-    const float local = __ldcg(p);
-    *p = run;
-    run += local;
+  for (int e = e0; e < elems; e += stride) {
+    // 4. totals of the ranks before (after) this one, from this GPU's own inbox
+    float remote = 0.f;
+    for (int s = lo; s < hi; ++s)
+      remote += __ldcg(xp.inbox[xp.rank] + (static_cast<size_t>(parity) * xp.world + s) * state_elems +
+                       static_cast<size_t>(bh) * elems + e);
+    // 5. segment prefixes on top of it
+    float run = remote;
+    for (int g = 0; g < xp.nseg; ++g) {
+      float* p = head_ws + static_cast<size_t>(g) * elems + e;
+      const float local = __ldcg(p);
+      *p = run;
+      run += local;
+    }
+    const int col = e / xp.rows, row = e % xp.rows;  // scratch layout [col][row] -> caller [row][col]
+    const size_t ext_idx = static_cast<size_t>(bh) * elems + static_cast<size_t>(row) * xp.cols + col;
+    if (xp.remote_out) xp.remote_out[ext_idx] = remote;
+    if (xp.inclusive_out) xp.inclusive_out[ext_idx] = run;
   }
-  const int col = e / xp.rows, row = e % xp.rows;  // scratch layout [col][row] -> caller [row][col]
-  const size_t ext_idx = static_cast<size_t>(bh) * elems + static_cast<size_t>(row) * xp.cols + col;
-  if (xp.remote_out) xp.remote_out[ext_idx] = remote;
-  if (xp.inclusive_out) xp.inclusive_out[ext_idx] = run;
 }
 
 // ---------------------------------------------------------------- row padding
@@ -1162,8 +1170,13 @@ int fla_sm100_state_exchange(const FlaArgs* a, int which, const FlaExchange* x) 
   xp.remote_out = x->remote_out;
   xp.inclusive_out = x->inclusive_out;
   xp.status = a->status;
+  // Blocks per head: few enough that all blocks of all heads are resident together (four per SM),
+  // but at most 16 elements per thread. The same on every rank (it indexes the flags).
   const int elems = da * dc;
-  fla_state_exchange_kernel<<<dim3((elems + 255) / 256, bh, 1), 256, 0, stream>>>(xp);
+  const int full = (elems + 255) / 256;
+  int bx = std::min(full, std::max(1, 592 / bh));
+  bx = std::max(bx, (full + 15) / 16);
+  fla_state_exchange_kernel<<<dim3(bx, bh, 1), 256, 0, stream>>>(xp);
   ++g_last_launches;
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) FLA_LOG_FAILURE("launch of fla_state_exchange_kernel failed: %s", cudaGetErrorString(e));
