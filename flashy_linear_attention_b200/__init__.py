@@ -6,9 +6,15 @@ flashlinear/kernels/__init__.py:1-5):
     linear_flash_wrapper_fwd, linear_flash_wrapper_bwd,
     linear_flash_wrapper_fwd_smallv_hd, linear_flash_wrapper_bwd_smallv_hd
 plus the lower-level causal_dot_product_fwd / causal_dot_product_bwd (running-state arguments),
-LinearAttentionResumable (state carried across calls) and host.HostPipeline (pinned host tensors).
+LinearAttentionResumable (state carried across calls), LinearAttentionNormalized (the README's
+denominator fused into streaming kernels) and host.HostPipeline (pinned host tensors).
 """
-from .functions import LinearAttention, LinearAttentionResumable, LinearAttentionSmallVHD
+from .functions import (
+    LinearAttention,
+    LinearAttentionNormalized,
+    LinearAttentionResumable,
+    LinearAttentionSmallVHD,
+)
 from .ops import (
     causal_dot_product_bwd,
     causal_dot_product_fwd,
@@ -24,6 +30,7 @@ __all__ = [
     "LinearAttention",
     "LinearAttentionSmallVHD",
     "LinearAttentionResumable",
+    "LinearAttentionNormalized",
     "linear_flash_wrapper_fwd",
     "linear_flash_wrapper_bwd",
     "linear_flash_wrapper_fwd_smallv_hd",

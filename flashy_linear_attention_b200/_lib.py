@@ -11,7 +11,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libflashlinear_sm100.so")
 
-FLA_ABI_VERSION = 5
+FLA_ABI_VERSION = 6
 FLA_MAX_RANKS = 8
 
 
@@ -76,6 +76,10 @@ EXPORTED_SYMBOLS = (
     "fla_sm100_state",
     "fla_sm100_fwd_static_scratch",
     "fla_sm100_product",
+    "fla_sm100_normalize_workspace_bytes",
+    "fla_sm100_normalize_fwd",
+    "fla_sm100_normalize_bwd_prepare",
+    "fla_sm100_normalize_bwd_sweep",
     "fla_sm100_pad_rows",
     "fla_sm100_unpad_rows",
     "fla_sm100_exchange_bytes",
@@ -125,6 +129,14 @@ def load() -> ctypes.CDLL:
         fn.restype = ctypes.c_int
         fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
                        ctypes.c_void_p]
+    lib.fla_sm100_normalize_workspace_bytes.restype = ctypes.c_size_t
+    lib.fla_sm100_normalize_workspace_bytes.argtypes = [ctypes.POINTER(FlaArgs)]
+    lib.fla_sm100_normalize_fwd.restype = ctypes.c_int
+    lib.fla_sm100_normalize_fwd.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_float, ctypes.c_void_p]
+    lib.fla_sm100_normalize_bwd_prepare.restype = ctypes.c_int
+    lib.fla_sm100_normalize_bwd_prepare.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_void_p, ctypes.c_void_p]
+    lib.fla_sm100_normalize_bwd_sweep.restype = ctypes.c_int
+    lib.fla_sm100_normalize_bwd_sweep.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_void_p]
     lib.fla_sm100_exchange_bytes.restype = ctypes.c_int
     lib.fla_sm100_exchange_bytes.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_int,
                                              ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]

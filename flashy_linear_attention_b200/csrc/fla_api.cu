@@ -13,6 +13,7 @@
 #include "../../include/flashlinear_sm100.h"
 #include "fla_kernel.cuh"
 #include "fla_wide_kernel.cuh"
+#include "fla_normalize.cuh"
 
 #include <cuda_runtime.h>
 
@@ -410,6 +411,15 @@ int device_info(DeviceInfo** out) {
                                  fla::WideCfg<2>::SMEM_BYTES) == cudaSuccess;
       ok &= cudaFuncSetAttribute(fla::fla_wide_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  fla::WideCfg<3>::SMEM_BYTES) == cudaSuccess;
+      constexpr int kMaxSmem = 232448;
+      ok &= cudaFuncSetAttribute(fla::fla_normalize_fwd_kernel<16>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) == cudaSuccess;
+      ok &= cudaFuncSetAttribute(fla::fla_normalize_fwd_kernel<32>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) == cudaSuccess;
+      ok &= cudaFuncSetAttribute(fla::fla_normalize_bwd_sweep_kernel<16>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) == cudaSuccess;
+      ok &= cudaFuncSetAttribute(fla::fla_normalize_bwd_sweep_kernel<32>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) == cudaSuccess;
       d.attr_set[0] = d.attr_set[1] = ok;
       ready[dev].store(2, std::memory_order_release);
     } else {
@@ -971,6 +981,175 @@ int fla_sm100_unpad_rows(const void* src, void* dst, long long rows, int d, int 
       std::min<long long>((rows + kPadRowsPerBlock - 1) / kPadRowsPerBlock, 148 * 32));
   fla_unpad_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const unsigned short*>(src), static_cast<unsigned short*>(dst), rows, d, dpad);
+  ++g_last_launches;
+  return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
+
+namespace {
+fla::NormTensor norm_tensor(const FlaTensor& t) {
+  fla::NormTensor n;
+  n.ptr = t.ptr;
+  n.sb = t.stride_b;
+  n.sh = t.stride_h;
+  n.sn = t.stride_n;
+  return n;
+}
+// token tile of the normalisation kernels: small tiles keep three CTAs resident per SM
+int norm_tile(int dk, int dv) { return (dk <= 128 && dv <= 128) ? 32 : 16; }
+constexpr size_t kNormSmemLimit = 232448;
+
+// Sequence segments of the normalisation kernels: about three CTAs (heads x segments) per SM;
+// segments a multiple of 64 tokens and at least 256 tokens long. The forward kernel (three CTAs
+// resident per SM) gets no more CTAs than fit at once (round_up = false); the sweep kernel (six
+// resident, two sweeps) measured faster with the count rounded up.
+void norm_segments(const FlaArgs* a, int sm_count, bool round_up, int* seg_len, int* nseg) {
+  const int bh = a->batch * a->heads;
+  int want = round_up ? (3 * sm_count + bh - 1) / bh : (3 * sm_count) / bh;
+  const int max_seg = (a->seqlen + 255) / 256;
+  if (want > max_seg) want = max_seg;
+  if (want < 1) want = 1;
+  int len = (a->seqlen + want - 1) / want;
+  len = (len + 63) / 64 * 64;
+  *seg_len = len;
+  *nseg = (a->seqlen + len - 1) / len;
+}
+
+// Fills the geometry fields and launches the column-sum kernel for k (weighted = 0) or for
+// dden_i q_i (weighted = 1) into `out`.
+int launch_colsum(fla::NormParams p, int weighted, float* out, int bh, cudaStream_t stream) {
+  p.weighted = weighted;
+  p.sums_out = out;
+  fla::fla_colsum_kernel<<<dim3(p.nseg, bh, 1), fla::kNormThreads, 0, stream>>>(p);
+  ++g_last_launches;
+  return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
+}  // namespace
+
+size_t fla_sm100_normalize_workspace_bytes(const FlaArgs* a) {
+  if (a == nullptr || a->batch <= 0 || a->heads <= 0 || a->seqlen <= 0 || a->dk <= 0) return 0;
+  int sm = 148, dev = 0, seg_len = 0, nseg = 1;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev);
+  norm_segments(a, sm, true, &seg_len, &nseg);
+  return 2 * static_cast<size_t>(a->batch) * a->heads * nseg * a->dk * sizeof(float);
+}
+
+int fla_sm100_normalize_fwd(const FlaArgs* a, float eps, float* den) {
+  DeviceInfo* dev = nullptr;
+  g_last_launches = 0;
+  int rc = check_common(a, &dev);
+  if (rc) return rc;
+  if (den == nullptr) return FLA_ERR_INVALID;
+  if ((rc = check_operand(operand(a->q, a->dk), a->batch, a->heads)) ||
+      (rc = check_operand(operand(a->k, a->dk), a->batch, a->heads)) ||
+      (rc = check_operand(operand(a->o, a->dv), a->batch, a->heads)))
+    return rc;
+  const int tile = norm_tile(a->dk, a->dv);
+  const size_t smem = fla::norm_fwd_smem_bytes(a->dk, a->dv, tile);
+  if (smem > kNormSmemLimit || a->dk > 512) return FLA_ERR_UNSUPPORTED;
+  fla::NormParams p;
+  memset(&p, 0, sizeof(p));
+  norm_segments(a, dev->sm_count, false, &p.seg_len, &p.nseg);
+  const int bh = a->batch * a->heads;
+  const size_t sums_bytes = static_cast<size_t>(bh) * p.nseg * a->dk * sizeof(float);
+  if (p.nseg > 1 && (a->workspace == nullptr || a->workspace_bytes < sums_bytes)) return FLA_ERR_WORKSPACE;
+  p.q = norm_tensor(a->q);
+  p.k = norm_tensor(a->k);
+  p.x = norm_tensor(a->o);
+  p.den = den;
+  p.heads = a->heads;
+  p.n = a->seqlen;
+  p.dk = a->dk;
+  p.dv = a->dv;
+  p.eps = eps;
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  if (p.nseg > 1) {
+    float* sums = static_cast<float*>(a->workspace);
+    if ((rc = launch_colsum(p, 0, sums, bh, stream))) return rc;
+    p.sums = sums;
+  }
+  const dim3 grid(p.nseg, bh, 1);
+  if (tile == 32)
+    fla::fla_normalize_fwd_kernel<32><<<grid, fla::kNormThreads, smem, stream>>>(p);
+  else
+    fla::fla_normalize_fwd_kernel<16><<<grid, fla::kNormThreads, smem, stream>>>(p);
+  ++g_last_launches;
+  return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
+
+int fla_sm100_normalize_bwd_prepare(const FlaArgs* a, const float* den, float* dden) {
+  DeviceInfo* dev = nullptr;
+  g_last_launches = 0;
+  int rc = check_common(a, &dev);
+  if (rc) return rc;
+  if (den == nullptr || dden == nullptr) return FLA_ERR_INVALID;
+  if ((rc = check_operand(operand(a->d_o, a->dv), a->batch, a->heads)) ||
+      (rc = check_operand(operand(a->o, a->dv), a->batch, a->heads)) ||
+      (rc = check_operand(operand(a->d_v, a->dv), a->batch, a->heads)))
+    return rc;
+  fla::NormParams p;
+  memset(&p, 0, sizeof(p));
+  p.x = norm_tensor(a->d_o);
+  p.y = norm_tensor(a->o);
+  p.z = norm_tensor(a->d_v);
+  p.den = const_cast<float*>(den);
+  p.dden = dden;
+  p.heads = a->heads;
+  p.n = a->seqlen;
+  p.dk = a->dk;
+  p.dv = a->dv;
+  // blocks per head: enough warps for about eight blocks per SM, at most one warp step per block
+  const int bh = a->batch * a->heads;
+  int bx = std::max(1, (148 * 8 + bh - 1) / bh);
+  bx = std::min(bx, std::max(1, (a->seqlen + 7) / 8));
+  fla::fla_normalize_bwd_prepare_kernel<<<dim3(bx, bh, 1), fla::kNormThreads, 0,
+                                          static_cast<cudaStream_t>(a->stream)>>>(p);
+  ++g_last_launches;
+  return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
+
+int fla_sm100_normalize_bwd_sweep(const FlaArgs* a, const float* dden) {
+  DeviceInfo* dev = nullptr;
+  g_last_launches = 0;
+  int rc = check_common(a, &dev);
+  if (rc) return rc;
+  if (dden == nullptr) return FLA_ERR_INVALID;
+  if ((rc = check_operand(operand(a->q, a->dk), a->batch, a->heads)) ||
+      (rc = check_operand(operand(a->k, a->dk), a->batch, a->heads)) ||
+      (rc = check_operand(operand(a->d_q, a->dk), a->batch, a->heads)) ||
+      (rc = check_operand(operand(a->d_k, a->dk), a->batch, a->heads)))
+    return rc;
+  const int tile = norm_tile(a->dk, a->dv);
+  const size_t smem = fla::norm_sweep_smem_bytes(a->dk, tile);
+  if (smem > kNormSmemLimit || a->dk > 512) return FLA_ERR_UNSUPPORTED;
+  fla::NormParams p;
+  memset(&p, 0, sizeof(p));
+  norm_segments(a, dev->sm_count, true, &p.seg_len, &p.nseg);
+  const int bh = a->batch * a->heads;
+  const size_t sums_elems = static_cast<size_t>(bh) * p.nseg * a->dk;
+  if (p.nseg > 1 && (a->workspace == nullptr || a->workspace_bytes < 2 * sums_elems * sizeof(float)))
+    return FLA_ERR_WORKSPACE;
+  p.q = norm_tensor(a->q);
+  p.k = norm_tensor(a->k);
+  p.dq = norm_tensor(a->d_q);
+  p.dk_ = norm_tensor(a->d_k);
+  p.dden = const_cast<float*>(dden);
+  p.heads = a->heads;
+  p.n = a->seqlen;
+  p.dk = a->dk;
+  p.dv = a->dv;
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  if (p.nseg > 1) {
+    float* sums = static_cast<float*>(a->workspace);
+    if ((rc = launch_colsum(p, 0, sums, bh, stream))) return rc;
+    if ((rc = launch_colsum(p, 1, sums + sums_elems, bh, stream))) return rc;
+    p.sums = sums;
+    p.rsums = sums + sums_elems;
+  }
+  const dim3 grid(p.nseg, bh, 2);
+  if (tile == 32)
+    fla::fla_normalize_bwd_sweep_kernel<32><<<grid, fla::kNormThreads, smem, stream>>>(p);
+  else
+    fla::fla_normalize_bwd_sweep_kernel<16><<<grid, fla::kNormThreads, smem, stream>>>(p);
   ++g_last_launches;
   return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
 }

@@ -140,3 +140,46 @@ class LinearAttentionResumable(Function):
             s_init=None if s_init is None else s_init.view(flat),
             r_init=r_init, r_final=r_final, s_last=s_last)
         return dq, dk_, dv_, None if r_final is None else r_final.view(B, H, dk, dv)
+
+
+class LinearAttentionNormalized(Function):
+    """Causal linear attention WITH its denominator:
+    ``out_i = sum_{j<=i} (q_i . k_j) v_j / (q_i . sum_{j<=i} k_j + eps)``, i.e. the whole recipe of
+    the reference's README (README.md:27-30) in one Function. The product runs in the same kernels
+    as LinearAttention / LinearAttentionSmallVHD; the denominator, the division and their
+    gradients run in three streaming kernels with an fp32 running sum instead of PyTorch's
+    cumsum / multiply / sum / divide passes. ``apply(q, k, v, eps=1e-5)``; dv a multiple of 8.
+    """
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
+    def forward(ctx: Any, q, k, v, eps: float = 1e-5):
+        ops.check_forward_preconditions(q, v, smallv=q.shape[-1] != v.shape[-1])
+        if v.shape[-1] % 8 != 0:
+            raise NotImplementedError("LinearAttentionNormalized needs a value head dim that is a multiple of 8")
+        q, k = ops.kernel_view(q), ops.kernel_view(k)  # repacked once if the rows are not 16-byte multiples
+        B, H, _, dk = q.shape
+        need_grad = any(ctx.needs_input_grad[:3])
+        s_final = None
+        if need_grad and ops.backward_uses_final_state(q, v):
+            s_final = torch.empty(B * H, dk, v.shape[-1], dtype=torch.float32, device=q.device)
+        out = ops.causal_dot_product_fwd(q, k, v, s_final=s_final)
+        if not out.is_contiguous():
+            out = out.contiguous()
+        den = ops.normalize_fwd(q, k, out, eps)
+        ctx.has_state = s_final is not None
+        if ctx.has_state:
+            ctx.save_for_backward(q, k, v, out, den, s_final)
+        else:
+            ctx.save_for_backward(q, k, v, out, den)
+        return out
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx: Any, grad_output):
+        q, k, v, out, den = ctx.saved_tensors[:5]
+        s_final = ctx.saved_tensors[5] if ctx.has_state else None
+        dnum, dden = ops.normalize_bwd_prepare(grad_output, out, den)
+        dq, dk, dv = ops.causal_dot_product_bwd(dnum, q, k, v, s_last=s_final, keep_padded=True)
+        ops.normalize_bwd_sweep(q, k, dq, dk, dden)
+        return dq, dk, dv, None

@@ -331,6 +331,78 @@ def causal_dot_product_bwd(
     return dQ, dK, dV
 
 
+def _norm_args(ref: torch.Tensor, dk: int, dv: int) -> FlaArgs:
+    a = FlaArgs()
+    a.batch, a.heads, a.seqlen, a.dk, a.dv = ref.shape[0], ref.shape[1], ref.shape[2], dk, dv
+    a.stream = torch.cuda.current_stream(ref.device).cuda_stream
+    a.status = _status_word(ref.device).data_ptr()
+    return a
+
+
+def _norm_workspace(a: FlaArgs, device: torch.device) -> Optional[torch.Tensor]:
+    need = _lib.load().fla_sm100_normalize_workspace_bytes(ctypes.byref(a))
+    if need == 0:
+        return None
+    ws = torch.empty(need, dtype=torch.uint8, device=device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), need
+    return ws
+
+
+def _norm_check(rc: int, name: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"flashlinear: {name} returned {rc}: {_lib.strerror(rc)}")
+
+
+def normalize_fwd(q: torch.Tensor, k: torch.Tensor, num: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """Divides `num` (the unnormalised product, [B,H,N,dv] bf16) IN PLACE by the denominator of
+    README.md:27-30, den_i = q_i . sum_{j<=i} k_j + eps, and returns den as fp32 [B*H, N].
+    q, k, num must be addressable by the kernels (see kernel_view)."""
+    _check_inputs(q, k, num)
+    if not (_addressable(q) and _addressable(k) and _addressable(num)):
+        raise ValueError("flashlinear: normalize_fwd needs 16-byte aligned rows (use ops.kernel_view)")
+    B, H, N, dk = q.shape
+    den = torch.empty(B * H, N, dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        a = _norm_args(q, dk, num.shape[-1])
+        a.q, a.k, a.o = _desc(q), _desc(k), _desc(num)
+        ws = _norm_workspace(a, q.device)  # noqa: F841 (kept alive until the launches are queued)
+        _norm_check(_lib.load().fla_sm100_normalize_fwd(ctypes.byref(a), float(eps), den.data_ptr()),
+                    "fla_sm100_normalize_fwd")
+    return den
+
+
+def normalize_bwd_prepare(g: torch.Tensor, out: torch.Tensor, den: torch.Tensor):
+    """(dnum, dden) for upstream gradient g of the normalised output `out`: dnum = g / den (bf16,
+    the upstream gradient of the unnormalised product), dden = -(g . out) / den (fp32 [B*H, N])."""
+    _check_inputs(g, out)
+    g = _kernel_view(g)
+    B, H, N, dv = out.shape
+    dnum = _padded_empty(out.shape, out.dtype, out.device) if dv % 8 else torch.empty(
+        out.shape, dtype=out.dtype, device=out.device)
+    dden = torch.empty(B * H, N, dtype=torch.float32, device=out.device)
+    with torch.cuda.device(out.device):
+        a = _norm_args(out, dv, dv)
+        a.d_o, a.o, a.d_v = _desc(g), _desc(out), _desc(dnum)
+        _norm_check(_lib.load().fla_sm100_normalize_bwd_prepare(ctypes.byref(a), den.data_ptr(), dden.data_ptr()),
+                    "fla_sm100_normalize_bwd_prepare")
+    return dnum, dden
+
+
+def normalize_bwd_sweep(q: torch.Tensor, k: torch.Tensor, dq: torch.Tensor, dk: torch.Tensor,
+                        dden: torch.Tensor) -> None:
+    """Adds the denominator's gradient to dq and dk in place:
+    dq_i += dden_i * sum_{j<=i} k_j,  dk_j += sum_{i>=j} dden_i q_i."""
+    _check_inputs(q, k, dq, dk)
+    if not all(_addressable(t) for t in (q, k, dq, dk)):
+        raise ValueError("flashlinear: normalize_bwd_sweep needs 16-byte aligned rows (use ops.kernel_view)")
+    with torch.cuda.device(q.device):
+        a = _norm_args(q, q.shape[-1], q.shape[-1])
+        a.q, a.k, a.d_q, a.d_k = _desc(q), _desc(k), _desc(dq), _desc(dk)
+        ws = _norm_workspace(a, q.device)  # noqa: F841
+        _norm_check(_lib.load().fla_sm100_normalize_bwd_sweep(ctypes.byref(a), dden.data_ptr()),
+                    "fla_sm100_normalize_bwd_sweep")
+
+
 def backward_uses_final_state(q: torch.Tensor, v: torch.Tensor) -> bool:
     """True when the backward of this shape runs unsegmented, i.e. can take the forward's final
     state (`s_last`) and sweep q, k, v, dO once for all three gradients."""

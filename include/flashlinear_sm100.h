@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define FLA_ABI_VERSION 5
+#define FLA_ABI_VERSION 6
 
 enum {
   FLA_OK = 0,
@@ -191,6 +191,29 @@ int fla_sm100_pad_rows(const void* src, void* dst, long long rows, int d, int dp
 /* dst[r][0..d) = src[r][0..d) for src rows of dpad elements: the inverse copy, for gradients that
  * must come back in the contiguous layout of torch.empty_like (linear_attn_kernels_smallv_hd.py:384). */
 int fla_sm100_unpad_rows(const void* src, void* dst, long long rows, int d, int dpad, void* stream);
+
+/* ---- normalised attention: the denominator of README.md:27-30 as kernels ----
+ * The reference returns the unnormalised product and leaves
+ *     denom = (q * k.cumsum(-2)).sum(-1, keepdim=True) + eps;  out = num / denom
+ * to PyTorch (several full-tensor passes, the cumulative sum in bf16). These three calls do it in
+ * one sweep per tensor with an fp32 running sum; they are opt-in (LinearAttentionNormalized in the
+ * Python layer) and change nothing about fla_sm100_fwd / fla_sm100_bwd.
+ *
+ * normalize_fwd: args->q, k (dk) and args->o (dv) holding the unnormalised product; on return
+ *   args->o holds o / den (in place) and den[b*heads + h][i] = q_i . sum_{j<=i} k_j + eps (fp32).
+ * normalize_bwd_prepare: args->d_o = gradient g of the normalised output, args->o = the normalised
+ *   output; writes args->d_v = g / den (the upstream gradient of the product, feed it to
+ *   fla_sm100_bwd as d_o) and dden[..][i] = -(g_i . o_i) / den_i.
+ * normalize_bwd_sweep: adds the denominator's part to the gradients fla_sm100_bwd produced, in
+ *   place: d_q[i] += dden_i * sum_{j<=i} k_j,  d_k[j] += sum_{i>=j} dden_i q_i  (reads q, k).
+ * Long sequences are cut into segments that run as separate CTAs; a column-sum kernel first gives
+ * every segment its starting sums. normalize_fwd and normalize_bwd_sweep therefore take scratch
+ * in args->workspace (fla_sm100_normalize_workspace_bytes(), pure scratch: nothing is kept in it
+ * between calls). Head dims up to 512. */
+size_t fla_sm100_normalize_workspace_bytes(const FlaArgs* args);
+int fla_sm100_normalize_fwd(const FlaArgs* args, float eps, float* den);
+int fla_sm100_normalize_bwd_prepare(const FlaArgs* args, const float* den, float* dden);
+int fla_sm100_normalize_bwd_sweep(const FlaArgs* args, const float* dden);
 
 /* Forward pass for callers that cannot obtain device memory themselves.
  * It has no counterpart in the reference (whose wrappers allocate through torch).

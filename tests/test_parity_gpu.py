@@ -502,3 +502,70 @@ def test_resumable_function_carries_state_and_gradients(shape):
     gk2, gv2 = torch.autograd.grad((s * w).sum(), (tk, tv))
     _check("dk from the state", _np(gk2), np.matmul(v64, np.swapaxes(w.double().cpu().numpy(), -1, -2)))
     _check("dv from the state", _np(gv2), np.matmul(k64, w.double().cpu().numpy()))
+
+
+def test_normalized_function_against_the_reference_denominator_fixture():
+    """LinearAttentionNormalized (product + denominator kernels) against the fixture that holds the
+    reference's naive path followed by the README's denominator (README.md:27-30), cfg1."""
+    from flashy_linear_attention_b200 import LinearAttentionNormalized
+
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    g = np.load(os.path.join(here, "ref_cfg1_b2h4_n256_d64_fp32_denominator.npz"))
+    B, H, N, dk, dv = (int(x) for x in g["shape"])
+    rng = np.random.Generator(np.random.PCG64(int(g["seed"])))
+    xq = rng.standard_normal((B, H, N, dk)).astype(np.float32)
+    xk = rng.standard_normal((B, H, N, dk)).astype(np.float32)
+    v = rng.standard_normal((B, H, N, dv)).astype(np.float32)
+    dy = rng.standard_normal((B, H, N, dv)).astype(np.float32)
+    q = torch.from_numpy(orc.elu_plus_one(xq)).to(DEV).requires_grad_(True)
+    k = torch.from_numpy(orc.elu_plus_one(xk)).to(DEV).requires_grad_(True)
+    vv = torch.from_numpy(v).to(DEV).requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        res = LinearAttentionNormalized.apply(q, k, vv, 1e-5)
+    assert res.dtype == torch.bfloat16
+    res.backward(torch.from_numpy(dy).to(DEV).to(torch.bfloat16))
+    torch.cuda.synchronize()
+    _ops().check_status(DEV)
+    rows = slice(None, None, int(g["row_stride"]))
+    for name, got in (("out", res), ("dq", q.grad), ("dk", k.grad), ("dv", vv.grad)):
+        mr = orc.max_rel_error(_np(got)[..., rows, :], g[name])
+        assert mr <= MAX_REL_TOL * 1.5, (name, mr)  # fp32 fixture inputs are rounded to bf16 here
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 512, 128, 128), (2, 3, 320, 64, 64), (1, 2, 256, 96, 32),
+                                   (1, 2, 256, 273, 64), (1, 1, 192, 83, 16), (1, 1, 2048, 128, 128)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_normalized_function_against_oracle(shape):
+    """Forward and all three gradients of the normalised attention vs the closed-form oracle."""
+    from flashy_linear_attention_b200 import LinearAttentionNormalized
+
+    B, H, N, dk, dv = shape
+    rng = np.random.default_rng(dk + 7 * dv)
+    q = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, dk))).astype(np.float32))
+    k = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, dk))).astype(np.float32))
+    v = orc.bf16_round(rng.standard_normal((B, H, N, dv)).astype(np.float32))
+    dy = orc.bf16_round(rng.standard_normal((B, H, N, dv)).astype(np.float32))
+    tq, tk, tv = (_to_dev(t).requires_grad_(True) for t in (q, k, v))
+    out = LinearAttentionNormalized.apply(tq, tk, tv, 1e-5)
+    gq, gk, gv = torch.autograd.grad(out, (tq, tk, tv), _to_dev(dy))
+    torch.cuda.synchronize()
+    _ops().check_status(DEV)
+    q64, k64, v64, dy64 = (t.astype(np.float64) for t in (q, k, v, dy))
+    _check("out", _np(out), orc.normalised_ref(q64, k64, v64))
+    rq, rk, rv = orc.normalised_ref_grads(q64, k64, v64, dy64)
+    _check("dv", _np(gv), rv)
+    # dQ and dK of the normalised attention are the SUM of the product's gradient (rounded to bf16
+    # by the product kernels, as in the reference's recipe) and the denominator's part, which
+    # largely cancel: |product part| is 2-6 x |sum| at these shapes, and so is the amplification of
+    # the product's 2e-3 rounding error. Tolerance for these two: twice the usual.
+    for name, got, want in (("dq", gq, rq), ("dk", gk, rk)):
+        mr = orc.max_rel_error(_np(got), want)
+        fr = orc.frobenius_rel_error(_np(got), want)
+        assert mr <= 2 * MAX_REL_TOL and fr < 2 * FROB_TOL, f"{name}: max-rel {mr:.3e}, frobenius {fr:.3e}"
+    # the denominator itself, fp32: q . cumsum(k) + eps
+    ops = _ops()
+    qv, kv = ops.kernel_view(_to_dev(q)), ops.kernel_view(_to_dev(k))
+    num = torch.ones(B, H, N, 8, dtype=torch.bfloat16, device=DEV)
+    den = ops.normalize_fwd(qv, kv, num, 1e-5)
+    torch.cuda.synchronize()
+    assert orc.max_rel_error(_np(den).reshape(B, H, N, 1), orc.denominator(q64, k64)) < 1e-5
