@@ -17,8 +17,9 @@ import torch
 
 warnings.filterwarnings("ignore")
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("FLASHLINEAR_REFERENCE", "/root/reference")
-sys.path.insert(0, REF)
+REF = os.environ.get("FLASHLINEAR_REFERENCE")  # or put the reference checkout on PYTHONPATH
+if REF:
+    sys.path.insert(0, REF)
 from flashlinear.test_attn import linear_ref_torch  # noqa: E402  (the reference's oracle)
 
 
