@@ -58,6 +58,28 @@ def measured_peaks():
         return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
+def measured_tensor_peak():
+    """Dense bf16 TFLOP/s of a cuBLAS GEMM on this pool: the sustained figure (the bench's timed
+    region is a long loop under the power cap), else the stated fallback."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["bf16_tflops_sustained"]), "measured sustained (MEASURED_PEAKS.json)"
+    except Exception:
+        return 1400.0, "fallback (1.4 PFLOP/s sustained, earlier measurement on this pool)"
+
+
+def algorithmic_flops(B, H, N, dk, dv, chunk=128):
+    """Tensor-core flops per step of the chunked algorithm with dense 128-token tiles: forward
+    2C*dk + 2C*dv + 4*dk*dv per token-head (score tile, tile x values, state read and update),
+    backward 6C*dk + 4C*dv + 10*dk*dv (three products, two of them with dk-wide outputs)."""
+    th = B * H * N
+    fwd = th * (2 * chunk * dk + 2 * chunk * dv + 4 * dk * dv)
+    bwd = th * (6 * chunk * dk + 4 * chunk * dv + 10 * dk * dv)
+    return fwd, bwd
+
+
 def algorithmic_bytes(B, H, N, dk, dv):
     """Compulsory HBM bytes per step, bf16: fwd reads q,k,v and writes o; bwd reads q,k,v,dO and
     writes dQ,dK,dV."""
@@ -438,6 +460,8 @@ def main():
     if rank == 0:
         peak, peak_src = measured_peaks()
         fwd_b, bwd_b = algorithmic_bytes(Bl, Hl, Nl, dk, dv)  # this rank's share
+        fwd_f, bwd_f = algorithmic_flops(Bl, Hl, Nl, dk, dv)
+        tpeak, tpeak_src = measured_tensor_peak()
         achieved = (fwd_b + bwd_b) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9
         traffic = NCU_TRAFFIC_BYTES_PER_STEP.get(args.workload) if world == 1 else None
         line = {
@@ -480,8 +504,13 @@ def main():
                 "peak_source": peak_src,
                 "algorithmic_bytes_per_step": fwd_b + bwd_b,
                 "traffic": traffic,
-                "fwd": {"ms": fwd_ms, "GBps": fwd_b / (fwd_ms * 1e-3) / 1e9, "frac": fwd_b / (fwd_ms * 1e-3) / 1e9 / peak},
+                "fwd": {"ms": fwd_ms, "GBps": fwd_b / (fwd_ms * 1e-3) / 1e9, "frac": fwd_b / (fwd_ms * 1e-3) / 1e9 / peak,
+                        "Mtokens_per_s": global_batch * N / (fwd_ms * 1e-3) / 1e6},
                 "bwd": {"ms": bwd_ms, "GBps": bwd_b / (bwd_ms * 1e-3) / 1e9, "frac": bwd_b / (bwd_ms * 1e-3) / 1e9 / peak},
+                # the same step against the tensor-pipe bound (the path is HBM-bound; shown beside it)
+                "tensor": {"achieved": (fwd_f + bwd_f) / ((fwd_ms + bwd_ms) * 1e-3) / 1e12, "peak": tpeak,
+                           "unit": "TFLOP/s", "frac": (fwd_f + bwd_f) / ((fwd_ms + bwd_ms) * 1e-3) / 1e12 / tpeak,
+                           "peak_source": tpeak_src, "algorithmic_flops_per_step": fwd_f + bwd_f},
             },
         }
         if world == 1 and not args.no_cpu_baseline:
