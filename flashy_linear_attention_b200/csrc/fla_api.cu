@@ -412,14 +412,17 @@ int device_info(DeviceInfo** out) {
       ok &= cudaFuncSetAttribute(fla::fla_wide_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  fla::WideCfg<3>::SMEM_BYTES) == cudaSuccess;
       constexpr int kMaxSmem = 232448;
-      ok &= cudaFuncSetAttribute(fla::fla_normalize_fwd_kernel<16>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) == cudaSuccess;
-      ok &= cudaFuncSetAttribute(fla::fla_normalize_fwd_kernel<32>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) == cudaSuccess;
-      ok &= cudaFuncSetAttribute(fla::fla_normalize_bwd_sweep_kernel<16>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) == cudaSuccess;
-      ok &= cudaFuncSetAttribute(fla::fla_normalize_bwd_sweep_kernel<32>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) == cudaSuccess;
+      auto big_smem = [&](const void* fn) {
+        ok &= cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) == cudaSuccess;
+      };
+      big_smem(reinterpret_cast<const void*>(fla::fla_normalize_fwd_kernel<32, 0>));
+      big_smem(reinterpret_cast<const void*>(fla::fla_normalize_fwd_kernel<32, 64>));
+      big_smem(reinterpret_cast<const void*>(fla::fla_normalize_fwd_kernel<32, 128>));
+      big_smem(reinterpret_cast<const void*>(fla::fla_normalize_fwd_kernel<16, 0>));
+      big_smem(reinterpret_cast<const void*>(fla::fla_normalize_bwd_sweep_kernel<32, 0>));
+      big_smem(reinterpret_cast<const void*>(fla::fla_normalize_bwd_sweep_kernel<32, 64>));
+      big_smem(reinterpret_cast<const void*>(fla::fla_normalize_bwd_sweep_kernel<32, 128>));
+      big_smem(reinterpret_cast<const void*>(fla::fla_normalize_bwd_sweep_kernel<16, 0>));
       d.attr_set[0] = d.attr_set[1] = ok;
       ready[dev].store(2, std::memory_order_release);
     } else {
@@ -1068,10 +1071,15 @@ int fla_sm100_normalize_fwd(const FlaArgs* a, float eps, float* den) {
     p.sums = sums;
   }
   const dim3 grid(p.nseg, bh, 1);
-  if (tile == 32)
-    fla::fla_normalize_fwd_kernel<32><<<grid, fla::kNormThreads, smem, stream>>>(p);
+  const int fixed = (a->dk == a->dv && (a->dk == 64 || a->dk == 128)) ? a->dk : 0;
+  if (fixed == 128)
+    fla::fla_normalize_fwd_kernel<32, 128><<<grid, fla::kNormThreads, smem, stream>>>(p);
+  else if (fixed == 64)
+    fla::fla_normalize_fwd_kernel<32, 64><<<grid, fla::kNormThreads, smem, stream>>>(p);
+  else if (tile == 32)
+    fla::fla_normalize_fwd_kernel<32, 0><<<grid, fla::kNormThreads, smem, stream>>>(p);
   else
-    fla::fla_normalize_fwd_kernel<16><<<grid, fla::kNormThreads, smem, stream>>>(p);
+    fla::fla_normalize_fwd_kernel<16, 0><<<grid, fla::kNormThreads, smem, stream>>>(p);
   ++g_last_launches;
   return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
 }
@@ -1101,8 +1109,13 @@ int fla_sm100_normalize_bwd_prepare(const FlaArgs* a, const float* den, float* d
   const int bh = a->batch * a->heads;
   int bx = std::max(1, (148 * 8 + bh - 1) / bh);
   bx = std::min(bx, std::max(1, (a->seqlen + 7) / 8));
-  fla::fla_normalize_bwd_prepare_kernel<<<dim3(bx, bh, 1), fla::kNormThreads, 0,
-                                          static_cast<cudaStream_t>(a->stream)>>>(p);
+  cudaStream_t stream = static_cast<cudaStream_t>(a->stream);
+  if (a->dv == 128)
+    fla::fla_normalize_bwd_prepare_kernel<128><<<dim3(bx, bh, 1), fla::kNormThreads, 0, stream>>>(p);
+  else if (a->dv == 64)
+    fla::fla_normalize_bwd_prepare_kernel<64><<<dim3(bx, bh, 1), fla::kNormThreads, 0, stream>>>(p);
+  else
+    fla::fla_normalize_bwd_prepare_kernel<0><<<dim3(bx, bh, 1), fla::kNormThreads, 0, stream>>>(p);
   ++g_last_launches;
   return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
 }
@@ -1146,10 +1159,15 @@ int fla_sm100_normalize_bwd_sweep(const FlaArgs* a, const float* dden) {
     p.rsums = sums + sums_elems;
   }
   const dim3 grid(p.nseg, bh, 2);
-  if (tile == 32)
-    fla::fla_normalize_bwd_sweep_kernel<32><<<grid, fla::kNormThreads, smem, stream>>>(p);
+  const int fixed = (a->dk == 64 || a->dk == 128) ? a->dk : 0;  // only dk matters to the sweep
+  if (fixed == 128 && tile == 32)
+    fla::fla_normalize_bwd_sweep_kernel<32, 128><<<grid, fla::kNormThreads, smem, stream>>>(p);
+  else if (fixed == 64 && tile == 32)
+    fla::fla_normalize_bwd_sweep_kernel<32, 64><<<grid, fla::kNormThreads, smem, stream>>>(p);
+  else if (tile == 32)
+    fla::fla_normalize_bwd_sweep_kernel<32, 0><<<grid, fla::kNormThreads, smem, stream>>>(p);
   else
-    fla::fla_normalize_bwd_sweep_kernel<16><<<grid, fla::kNormThreads, smem, stream>>>(p);
+    fla::fla_normalize_bwd_sweep_kernel<16, 0><<<grid, fla::kNormThreads, smem, stream>>>(p);
   ++g_last_launches;
   return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
 }

@@ -164,10 +164,14 @@ __host__ __device__ inline size_t norm_fwd_smem_bytes(int dk, int dv, int tile) 
   return kNormStages * tile * (2 * dkp + dvp) * 2 + tile * dkp * 4 + kNormThreads * 8;  // + group totals
 }
 
-template <int T>
+// D: compile-time head dim when dk == dv == D (strides, divisions and loop counts then fold to
+// constants), 0: head dims taken from the parameters at run time.
+template <int T, int D>
 __global__ void __launch_bounds__(kNormThreads)
-fla_normalize_fwd_kernel(const NormParams p) {
+fla_normalize_fwd_kernel(const NormParams p_in) {
   constexpr int kNormTile = T;  // shadows the default tile size inside this kernel
+  NormParams p = p_in;
+  if (D != 0) p.dk = p.dv = D;
   extern __shared__ __align__(16) uint8_t norm_smem[];
   const int seg = blockIdx.x, bh = blockIdx.y;
   const int b = bh / p.heads, h = bh % p.heads;
@@ -299,8 +303,11 @@ fla_normalize_fwd_kernel(const NormParams p) {
 
 // Per row: dnum = g / den, dden = -(g . out) / den. Grid (blocks, batch*heads); `lpr` lanes share
 // a row (8 columns per lane and step), the warps of a head's blocks stride over its tokens.
+template <int D>
 __global__ void __launch_bounds__(kNormThreads)
-fla_normalize_bwd_prepare_kernel(const NormParams p) {
+fla_normalize_bwd_prepare_kernel(const NormParams p_in) {
+  NormParams p = p_in;
+  if (D != 0) p.dk = p.dv = D;
   const int lane = threadIdx.x & 31;
   const int bh = blockIdx.y;
   const int b = bh / p.heads, h = bh % p.heads;
@@ -360,10 +367,12 @@ __host__ __device__ inline size_t norm_sweep_smem_bytes(int dk, int tile) {
 
 // blockIdx.z = 0: ascending sweep, z += k_i, dQ_i += dden_i z   (z includes token i)
 // blockIdx.z = 1: descending sweep, w += dden_i q_i, dK_i += w  (w includes token i)
-template <int T>
+template <int T, int D>
 __global__ void __launch_bounds__(kNormThreads)
-fla_normalize_bwd_sweep_kernel(const NormParams p) {
+fla_normalize_bwd_sweep_kernel(const NormParams p_in) {
   constexpr int kNormTile = T;
+  NormParams p = p_in;
+  if (D != 0) p.dk = p.dv = D;
   extern __shared__ __align__(16) uint8_t norm_smem[];
   const int seg = blockIdx.x, bh = blockIdx.y;
   const bool rev = blockIdx.z == 1;
