@@ -65,6 +65,22 @@ def test_invalid_arguments_are_rejected_without_a_gpu():
     assert need >= 2 * 4 * 128 * 128 * 4
     a.segments = 1
     assert lib.fla_sm100_workspace_bytes(ctypes.byref(a), 0) == 0
+    # the wide (SmallVHD) shapes never split the sequence: no scratch, one segment
+    a.dk, a.dv, a.segments = 273, 64, 0
+    assert lib.fla_sm100_workspace_bytes(ctypes.byref(a), 0) == 0
+    assert lib.fla_sm100_workspace_bytes(ctypes.byref(a), 1) == 0
+    assert lib.fla_sm100_auto_segments(ctypes.byref(a), 1) == 1
+    # entry points added beside the reference's interface reject null / empty arguments as well
+    z = FlaArgs()
+    assert lib.fla_sm100_normalize_fwd(None, 1e-5, None) == -1
+    assert lib.fla_sm100_normalize_fwd(ctypes.byref(z), 1e-5, None) == -1
+    assert lib.fla_sm100_normalize_bwd_prepare(ctypes.byref(z), None, None) == -1
+    assert lib.fla_sm100_normalize_bwd_sweep(ctypes.byref(z), None) == -1
+    assert lib.fla_sm100_normalize_workspace_bytes(None) == 0
+    assert lib.fla_sm100_pad_rows(None, None, 1, 8, 8, None) == -1
+    assert lib.fla_sm100_unpad_rows(None, None, 1, 8, 8, None) == -1
+    assert lib.fla_sm100_pad_rows(ctypes.c_void_p(16), ctypes.c_void_p(32), 4, 9, 12, None) == -3  # dpad % 8
+    assert lib.fla_sm100_pad_rows(ctypes.c_void_p(16), ctypes.c_void_p(32), 4, 9, 8, None) == -1   # dpad < d
 
 
 def test_wrappers_keep_reference_preconditions():
