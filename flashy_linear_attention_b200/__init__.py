@@ -14,6 +14,7 @@ from .functions import (
     LinearAttentionNormalized,
     LinearAttentionResumable,
     LinearAttentionSmallVHD,
+    TaylorLinearAttention,
 )
 from .ops import (
     causal_dot_product_bwd,
@@ -31,6 +32,7 @@ __all__ = [
     "LinearAttentionSmallVHD",
     "LinearAttentionResumable",
     "LinearAttentionNormalized",
+    "TaylorLinearAttention",
     "linear_flash_wrapper_fwd",
     "linear_flash_wrapper_bwd",
     "linear_flash_wrapper_fwd_smallv_hd",

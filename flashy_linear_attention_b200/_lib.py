@@ -11,7 +11,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libflashlinear_sm100.so")
 
-FLA_ABI_VERSION = 6
+FLA_ABI_VERSION = 7
 FLA_MAX_RANKS = 8
 
 
@@ -80,6 +80,9 @@ EXPORTED_SYMBOLS = (
     "fla_sm100_normalize_fwd",
     "fla_sm100_normalize_bwd_prepare",
     "fla_sm100_normalize_bwd_sweep",
+    "fla_sm100_taylor_dims",
+    "fla_sm100_taylor_features",
+    "fla_sm100_taylor_features_bwd",
     "fla_sm100_pad_rows",
     "fla_sm100_unpad_rows",
     "fla_sm100_exchange_bytes",
@@ -137,6 +140,14 @@ def load() -> ctypes.CDLL:
     lib.fla_sm100_normalize_bwd_prepare.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_void_p, ctypes.c_void_p]
     lib.fla_sm100_normalize_bwd_sweep.restype = ctypes.c_int
     lib.fla_sm100_normalize_bwd_sweep.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_void_p]
+    lib.fla_sm100_taylor_dims.restype = ctypes.c_int
+    lib.fla_sm100_taylor_dims.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
+    lib.fla_sm100_taylor_features.restype = ctypes.c_int
+    lib.fla_sm100_taylor_features.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int,
+                                              ctypes.c_void_p]
+    lib.fla_sm100_taylor_features_bwd.restype = ctypes.c_int
+    lib.fla_sm100_taylor_features_bwd.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                                  ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p]
     lib.fla_sm100_exchange_bytes.restype = ctypes.c_int
     lib.fla_sm100_exchange_bytes.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_int,
                                              ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]

@@ -16,7 +16,7 @@ LIB_NAME = "libflashlinear_sm100.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
 
 SOURCES = ["fla_api.cu"]
-HEADERS = ["fla_kernel.cuh", "fla_wide_kernel.cuh", "fla_normalize.cuh", "ptx.cuh", os.path.join("..", "..", "include", "flashlinear_sm100.h")]
+HEADERS = ["fla_kernel.cuh", "fla_wide_kernel.cuh", "fla_normalize.cuh", "fla_taylor.cuh", "ptx.cuh", os.path.join("..", "..", "include", "flashlinear_sm100.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -14,6 +14,7 @@
 #include "fla_kernel.cuh"
 #include "fla_wide_kernel.cuh"
 #include "fla_normalize.cuh"
+#include "fla_taylor.cuh"
 
 #include <cuda_runtime.h>
 
@@ -957,6 +958,70 @@ int fla_sm100_fwd_static_scratch(const FlaArgs* a) {
   return run_products(&p, 1, a->batch, a->heads, a->seqlen, a->dk, a->dv, nseg, scratch,
                       FLA_STATIC_SCRATCH_BYTES, a->status, static_cast<cudaStream_t>(a->stream),
                       *dev);
+}
+
+int fla_sm100_taylor_dims(int d, int* features, int* padded) {
+  if (d != 8 && d != 16) return FLA_ERR_UNSUPPORTED;
+  const int f = 1 + d + d * d;
+  if (features) *features = f;
+  if (padded) *padded = (f + 7) / 8 * 8;
+  return FLA_OK;
+}
+
+int fla_sm100_taylor_features(const void* x, void* phi, long long rows, int d, void* stream) {
+  (void)cudaGetLastError();
+  g_last_launches = 0;
+  if (x == nullptr || phi == nullptr || rows <= 0) return FLA_ERR_INVALID;
+  if (d != 8 && d != 16) return FLA_ERR_UNSUPPORTED;
+  if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || reinterpret_cast<uintptr_t>(phi) % 16 != 0)
+    return FLA_ERR_ALIGNMENT;
+  const int blocks = static_cast<int>(
+      std::min<long long>((rows + fla::kTaylorRows - 1) / fla::kTaylorRows, 148 * 16));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (d == 16) {
+    constexpr int smem = fla::taylor_tile_smem_bytes<16>();
+    if (cudaFuncSetAttribute(fla::fla_taylor_fwd_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             smem) != cudaSuccess)
+      return FLA_ERR_CUDA;
+    fla::fla_taylor_fwd_kernel<16><<<blocks, fla::kTaylorRows, smem, st>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<uint4*>(phi), rows);
+  } else {
+    constexpr int smem = fla::taylor_tile_smem_bytes<8>();
+    fla::fla_taylor_fwd_kernel<8><<<blocks, fla::kTaylorRows, smem, st>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<uint4*>(phi), rows);
+  }
+  ++g_last_launches;
+  return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
+
+int fla_sm100_taylor_features_bwd(const void* dphi, const void* x, void* dx, long long rows, int d,
+                                  void* stream) {
+  (void)cudaGetLastError();
+  g_last_launches = 0;
+  if (dphi == nullptr || x == nullptr || dx == nullptr || rows <= 0) return FLA_ERR_INVALID;
+  if (d != 8 && d != 16) return FLA_ERR_UNSUPPORTED;
+  if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || reinterpret_cast<uintptr_t>(dphi) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(dx) % 16 != 0)
+    return FLA_ERR_ALIGNMENT;
+  const int blocks = static_cast<int>(
+      std::min<long long>((rows + fla::kTaylorRows - 1) / fla::kTaylorRows, 148 * 16));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (d == 16) {
+    constexpr int smem = fla::taylor_tile_smem_bytes<16>();
+    e = cudaFuncSetAttribute(fla::fla_taylor_bwd_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return FLA_ERR_CUDA;
+    fla::fla_taylor_bwd_kernel<16><<<blocks, fla::kTaylorRows, smem, st>>>(
+        static_cast<const uint4*>(dphi), static_cast<const __nv_bfloat16*>(x),
+        static_cast<__nv_bfloat16*>(dx), rows);
+  } else {
+    constexpr int smem = fla::taylor_tile_smem_bytes<8>();
+    fla::fla_taylor_bwd_kernel<8><<<blocks, fla::kTaylorRows, smem, st>>>(
+        static_cast<const uint4*>(dphi), static_cast<const __nv_bfloat16*>(x),
+        static_cast<__nv_bfloat16*>(dx), rows);
+  }
+  ++g_last_launches;
+  return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
 }
 
 int fla_sm100_pad_rows(const void* src, void* dst, long long rows, int d, int dpad, void* stream) {

@@ -183,3 +183,32 @@ class LinearAttentionNormalized(Function):
         dq, dk, dv = ops.causal_dot_product_bwd(dnum, q, k, v, s_last=s_final, keep_padded=True)
         ops.normalize_bwd_sweep(q, k, dq, dk, dden)
         return dq, dk, dv, None
+
+
+class TaylorLinearAttention(Function):
+    """Causal linear attention on second-order Taylor features of RAW q, k:
+    ``apply(xq, xk, v)`` with xq, xk ``[B, H, N, d]`` (d = 8 or 16) and v ``[B, H, N, dv]`` (dv <= 64)
+    returns ``sum_{j<=i} (phi(xq_i) . phi(xk_j)) v_j`` with ``phi(x) = [1, x / d^(1/4),
+    vec(x x^T) / (sqrt(2) sqrt(d))]`` (benchmark configuration 4: d = 16 -> 273 features), and its
+    backward returns gradients with respect to the raw xq, xk and v.
+
+    The feature map runs in its own kernels and writes rows the attention kernels read in place,
+    so the pad passes of ``LinearAttentionSmallVHD`` on contiguous 273-wide tensors disappear and the
+    273-wide tensors never have to exist on the caller's side. The reference has no counterpart.
+    """
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
+    def forward(ctx: Any, xq, xk, v):
+        pq, pk = ops.taylor_features(xq), ops.taylor_features(xk)
+        ops.check_forward_preconditions(pq, v, smallv=True)
+        out = ops.causal_dot_product_fwd(pq, pk, v)
+        ctx.save_for_backward(xq, xk, v, pq, pk)
+        return out
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx: Any, grad_output):
+        xq, xk, v, pq, pk = ctx.saved_tensors
+        dpq, dpk, dv = ops.causal_dot_product_bwd(grad_output, pq, pk, v, keep_padded=True)
+        return ops.taylor_features_bwd(dpq, xq), ops.taylor_features_bwd(dpk, xk), dv

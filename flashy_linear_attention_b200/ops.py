@@ -403,6 +403,51 @@ def normalize_bwd_sweep(q: torch.Tensor, k: torch.Tensor, dq: torch.Tensor, dk: 
                     "fla_sm100_normalize_bwd_sweep")
 
 
+def taylor_features(x: torch.Tensor) -> torch.Tensor:
+    """Second-order Taylor features phi(x) = [1, x / d^(1/4), vec(x x^T) / (sqrt(2) sqrt(d))] of raw
+    x [B, H, N, d] (bf16, d = 8 or 16): a [B, H, N, 1 + d + d^2] view of rows padded to a multiple
+    of 8 elements, which the attention kernels read in place (no repack)."""
+    _check_inputs(x)
+    lib = _lib.load()
+    d = x.shape[-1]
+    f, fp = ctypes.c_int(0), ctypes.c_int(0)
+    if lib.fla_sm100_taylor_dims(d, ctypes.byref(f), ctypes.byref(fp)) != 0:
+        raise NotImplementedError("flashlinear: Taylor features are built for raw head dims 8 and 16")
+    xc = x.contiguous()
+    buf = torch.empty(x.shape[:-1] + (fp.value,), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib.fla_sm100_taylor_features(xc.data_ptr(), buf.data_ptr(), xc.numel() // d, d,
+                                           torch.cuda.current_stream(x.device).cuda_stream)
+    _norm_check(rc, "fla_sm100_taylor_features")
+    return buf[..., :f.value]
+
+
+def taylor_features_bwd(dphi: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """Gradient with respect to raw x of taylor_features(x) for feature gradients dphi
+    ([B, H, N, 1 + d + d^2], rows padded to a multiple of 8 elements as taylor_features returns
+    and as causal_dot_product_bwd(..., keep_padded=True) produces)."""
+    _check_inputs(dphi, x)
+    lib = _lib.load()
+    d = x.shape[-1]
+    f, fp = ctypes.c_int(0), ctypes.c_int(0)
+    if lib.fla_sm100_taylor_dims(d, ctypes.byref(f), ctypes.byref(fp)) != 0:
+        raise NotImplementedError("flashlinear: Taylor features are built for raw head dims 8 and 16")
+    rows = x.numel() // d
+    dense = (dphi.shape[-1] == f.value and dphi.stride(3) == 1 and dphi.stride(2) == fp.value
+             and dphi.stride(1) == fp.value * dphi.shape[2] and dphi.stride(0) == dphi.stride(1) * dphi.shape[1])
+    if not dense:  # bring the gradient into padded rows
+        buf = torch.zeros(dphi.shape[:-1] + (fp.value,), dtype=dphi.dtype, device=dphi.device)
+        buf[..., :f.value] = dphi
+        dphi = buf[..., :f.value]
+    xc = x.contiguous()
+    dx = torch.empty_like(xc)
+    with torch.cuda.device(x.device):
+        rc = lib.fla_sm100_taylor_features_bwd(dphi.data_ptr(), xc.data_ptr(), dx.data_ptr(), rows, d,
+                                               torch.cuda.current_stream(x.device).cuda_stream)
+    _norm_check(rc, "fla_sm100_taylor_features_bwd")
+    return dx
+
+
 def backward_uses_final_state(q: torch.Tensor, v: torch.Tensor) -> bool:
     """True when the backward of this shape runs unsegmented, i.e. can take the forward's final
     state (`s_last`) and sweep q, k, v, dO once for all three gradients."""

@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define FLA_ABI_VERSION 6
+#define FLA_ABI_VERSION 7
 
 enum {
   FLA_OK = 0,
@@ -214,6 +214,19 @@ size_t fla_sm100_normalize_workspace_bytes(const FlaArgs* args);
 int fla_sm100_normalize_fwd(const FlaArgs* args, float eps, float* den);
 int fla_sm100_normalize_bwd_prepare(const FlaArgs* args, const float* den, float* dden);
 int fla_sm100_normalize_bwd_sweep(const FlaArgs* args, const float* dden);
+
+/* ---- second-order Taylor feature map (benchmark configuration 4) ----
+ * phi(x) = [1, x / d^(1/4), vec(x x^T) / (sqrt(2) sqrt(d))]: 1 + d + d^2 features, so that
+ * phi(q) . phi(k) = 1 + s + s^2 / 2 with s = q . k / sqrt(d). The reference has no such code (its
+ * README links the idea only); d = 16 gives the 273 features fed to LinearAttentionSmallVHD.
+ * taylor_features writes bf16 rows of `padded` elements (the first `features` valid, the rest zero),
+ * i.e. rows the attention kernels address in place (pass stride_n = padded): no pad pass.
+ * taylor_features_bwd contracts gradients of such rows back to the d raw dimensions.
+ * x, dx: [rows][d] bf16 contiguous; phi, dphi: [rows][padded] bf16. d = 8 or 16. */
+int fla_sm100_taylor_dims(int d, int* features, int* padded);
+int fla_sm100_taylor_features(const void* x, void* phi, long long rows, int d, void* stream);
+int fla_sm100_taylor_features_bwd(const void* dphi, const void* x, void* dx, long long rows, int d,
+                                  void* stream);
 
 /* Forward pass for callers that cannot obtain device memory themselves.
  * It has no counterpart in the reference (whose wrappers allocate through torch).

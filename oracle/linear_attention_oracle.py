@@ -224,6 +224,16 @@ def taylor_feature_map(x: np.ndarray) -> np.ndarray:
     return np.concatenate([one, lin, quad.astype(x.dtype)], axis=-1)
 
 
+def taylor_feature_map_grad(x: np.ndarray, dphi: np.ndarray) -> np.ndarray:
+    """Gradient of sum(taylor_feature_map(x) * dphi) with respect to x (closed form):
+    dx_a = dphi_lin[a] / d^(1/4) + sum_b (dPhi[a, b] + dPhi[b, a]) x_b / (sqrt(2) sqrt(d))."""
+    d = x.shape[-1]
+    dlin = dphi[..., 1:1 + d]
+    dquad = dphi[..., 1 + d:1 + d + d * d].reshape(x.shape[:-1] + (d, d))
+    sym = dquad + np.swapaxes(dquad, -1, -2)
+    return dlin / (d ** 0.25) + np.einsum("...ab,...b->...a", sym, x) / (np.sqrt(2.0) * np.sqrt(d))
+
+
 def frobenius_rel_error(x: np.ndarray, y: np.ndarray) -> float:
     """|x - y|_F / |y|_F, the metric of flashlinear/test_attn.py:24-25."""
     x = np.asarray(x, dtype=np.float64)

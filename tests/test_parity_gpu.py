@@ -569,3 +569,55 @@ def test_normalized_function_against_oracle(shape):
     den = ops.normalize_fwd(qv, kv, num, 1e-5)
     torch.cuda.synchronize()
     assert orc.max_rel_error(_np(den).reshape(B, H, N, 1), orc.denominator(q64, k64)) < 1e-5
+
+
+@pytest.mark.parametrize("d", [8, 16])
+def test_taylor_feature_kernels_against_oracle(d):
+    """Feature map and its gradient kernel vs the numpy restatement (bf16 outputs, fp32 math)."""
+    ops = _ops()
+    rng = np.random.default_rng(d)
+    B, H, N = 2, 3, 200  # 1200 rows: not a multiple of the backward kernel's 128-row tiles
+    x = orc.bf16_round(rng.standard_normal((B, H, N, d)).astype(np.float32))
+    tx = _to_dev(x)
+    phi = ops.taylor_features(tx)
+    F = 1 + d + d * d
+    assert tuple(phi.shape) == (B, H, N, F) and phi.stride(2) % 8 == 0 and phi.stride(2) >= F
+    want = orc.taylor_feature_map(x.astype(np.float64))
+    assert orc.max_rel_error(_np(phi), want) <= 2.0 ** -8
+    whole = phi.as_strided((B * H * N, phi.stride(2)), (phi.stride(2), 1))
+    assert bool((whole[:, F:] == 0).all())
+    dphi = orc.bf16_round(rng.standard_normal((B, H, N, F)).astype(np.float32))
+    tdphi = torch.zeros_like(whole).view(B, H, N, -1)
+    tdphi[..., :F] = _to_dev(dphi)
+    dx = ops.taylor_features_bwd(tdphi[..., :F], tx)
+    dx2 = ops.taylor_features_bwd(_to_dev(dphi), tx)  # contiguous gradient: brought into padded rows first
+    torch.cuda.synchronize()
+    want_dx = orc.taylor_feature_map_grad(x.astype(np.float64), dphi.astype(np.float64))
+    assert orc.max_rel_error(_np(dx), want_dx) <= 2.0 ** -7
+    assert torch.equal(dx, dx2)
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 384, 16, 64), (2, 2, 256, 16, 32), (1, 2, 320, 8, 64)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_taylor_attention_function_against_oracle(shape):
+    """Raw q, k -> Taylor features -> causal product, forward and gradients w.r.t. the RAW inputs."""
+    from flashy_linear_attention_b200 import TaylorLinearAttention
+
+    B, H, N, d, dv = shape
+    rng = np.random.default_rng(31 * d + dv)
+    xq = orc.bf16_round(rng.standard_normal((B, H, N, d)).astype(np.float32))
+    xk = orc.bf16_round(rng.standard_normal((B, H, N, d)).astype(np.float32))
+    v = orc.bf16_round(rng.standard_normal((B, H, N, dv)).astype(np.float32))
+    dy = orc.bf16_round(rng.standard_normal((B, H, N, dv)).astype(np.float32))
+    tq, tk, tv = (_to_dev(t).requires_grad_(True) for t in (xq, xk, v))
+    out = TaylorLinearAttention.apply(tq, tk, tv)
+    gq, gk, gv = torch.autograd.grad(out, (tq, tk, tv), _to_dev(dy))
+    torch.cuda.synchronize()
+    _ops().check_status(DEV)
+    q64, k64, v64, dy64 = (t.astype(np.float64) for t in (xq, xk, v, dy))
+    pq, pk = orc.taylor_feature_map(q64), orc.taylor_feature_map(k64)
+    _check("out", _np(out), orc.linear_ref(pq, pk, v64))
+    dpq, dpk, rv = orc.linear_ref_grads(pq, pk, v64, dy64)
+    _check("dv", _np(gv), rv)
+    _check("dxq", _np(gq), orc.taylor_feature_map_grad(q64, dpq))
+    _check("dxk", _np(gk), orc.taylor_feature_map_grad(k64, dpk))
