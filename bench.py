@@ -267,6 +267,8 @@ def main():
                     help="sequence sharding: peer = state kernels store straight into the peers' memory over "
                          "NVLink and wait on flags (one fused kernel, no NCCL); nccl = all-gather + local sum")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch every kernel from Python instead of replaying a captured CUDA graph per pass")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -386,6 +388,22 @@ def main():
         launches_b = step_bwd()
     barrier()
     ops.check_status(device)
+    # The launches of a pass are captured in a CUDA graph and replayed (one graph per pass, so that
+    # the forward / backward split can still be timed with events). Not for the sequence-sharded
+    # path: its exchange kernel carries an epoch that changes with every call.
+    launch_mode = "eager"
+    if not seq_sharded and not args.no_graph:
+        try:
+            from flashy_linear_attention_b200.graphs import capture_step
+            g_fwd, g_bwd = capture_step(step_fwd), capture_step(step_bwd)
+            step_fwd, step_bwd = g_fwd, g_bwd
+            launch_mode = "one CUDA graph replay per pass"
+            for _ in range(3):
+                step_fwd(); step_bwd()
+            barrier()
+            ops.check_status(device)
+        except Exception as exc:  # capture is an optimisation of the host side only
+            launch_mode = f"eager (graph capture failed: {type(exc).__name__})"
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
     barrier()
     t_region0 = time.time()
@@ -484,6 +502,7 @@ def main():
                 f"batch*head sharded over {world} GPU(s): {Bl}x{Hl} heads per GPU, no collective",
                 "l2": f"per-GPU working set {8 * q.numel() * 2 / 1e6:.0f} MB exceeds the 126 MB L2; no flush between steps",
                 "chunk": 128,
+                "launch": launch_mode,
             },
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_all,
                     "d2h_bytes_per_step": d2h_all, "steps": e2e_steps,
