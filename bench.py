@@ -389,10 +389,11 @@ def main():
     barrier()
     ops.check_status(device)
     # The launches of a pass are captured in a CUDA graph and replayed (one graph per pass, so that
-    # the forward / backward split can still be timed with events). Not for the sequence-sharded
-    # path: its exchange kernel carries an epoch that changes with every call.
+    # the forward / backward split can still be timed with events). The sequence-sharded path is
+    # captured too when it uses the fused peer exchange (its exchange count lives on the device);
+    # the NCCL arm stays eager.
     launch_mode = "eager"
-    if not seq_sharded and not args.no_graph:
+    if (not seq_sharded or peer_ex is not None) and not args.no_graph:
         try:
             from flashy_linear_attention_b200.graphs import capture_step
             g_fwd, g_bwd = capture_step(step_fwd), capture_step(step_bwd)

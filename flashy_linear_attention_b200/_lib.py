@@ -11,7 +11,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libflashlinear_sm100.so")
 
-FLA_ABI_VERSION = 7
+FLA_ABI_VERSION = 8
 FLA_MAX_RANKS = 8
 
 
@@ -63,6 +63,7 @@ class FlaExchange(ctypes.Structure):
         ("flags", ctypes.c_void_p * 8),
         ("remote_out", ctypes.c_void_p),
         ("inclusive_out", ctypes.c_void_p),
+        ("epoch_counter", ctypes.c_void_p),
     ]
 
 

@@ -201,7 +201,11 @@ struct ExchangeParams {
   float* remote_out;
   float* inclusive_out;
   int* status;
+  const unsigned* epoch_counter;  // device-side count (epoch = *epoch_counter + 1), or null
 };
+
+// Stores the epoch an exchange kernel just used back into its device-side counter.
+__global__ void fla_exchange_bump_kernel(unsigned* counter) { *counter = *counter + 1u; }
 
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
   unsigned v;
@@ -224,7 +228,9 @@ __global__ void fla_state_exchange_kernel(const ExchangeParams xp) {
   const int elems = xp.rows * xp.cols;
   const int e0 = blockIdx.x * blockDim.x + threadIdx.x;
   const int stride = gridDim.x * blockDim.x;
-  const unsigned parity = xp.epoch & 1u;
+  // every block reads the same count: it only changes in the one-thread kernel behind this one
+  const unsigned epoch = xp.epoch_counter != nullptr ? __ldcg(xp.epoch_counter) + 1u : xp.epoch;
+  const unsigned parity = epoch & 1u;
   const size_t nblocks = static_cast<size_t>(gridDim.x) * gridDim.y;
   const size_t block_id = static_cast<size_t>(bh) * gridDim.x + blockIdx.x;
   const size_t state_elems = static_cast<size_t>(xp.bh_count) * elems;
@@ -247,7 +253,7 @@ __global__ void fla_state_exchange_kernel(const ExchangeParams xp) {
   __syncthreads();
   if (static_cast<int>(threadIdx.x) < xp.world && static_cast<int>(threadIdx.x) != xp.rank) {
     const size_t f = (static_cast<size_t>(parity) * xp.world + xp.rank) * nblocks + block_id;
-    st_relaxed_sys(xp.flags[threadIdx.x] + f, xp.epoch);
+    st_relaxed_sys(xp.flags[threadIdx.x] + f, epoch);
   }
   // 3. wait (bounded) for the same block of every other rank. Waiting for all of them, not only the
   //    ones whose totals are needed, keeps any rank from running two exchanges ahead of another,
@@ -259,7 +265,7 @@ __global__ void fla_state_exchange_kernel(const ExchangeParams xp) {
     const unsigned* f = xp.flags[xp.rank] +
                         (static_cast<size_t>(parity) * xp.world + threadIdx.x) * nblocks + block_id;
     const long long t0 = clock64();
-    while (ld_acquire_sys(f) != xp.epoch) {
+    while (ld_acquire_sys(f) != epoch) {
       if (clock64() - t0 > fla::ptx::kWaitLimitCycles) {
         timed_out = 1;
         break;
@@ -1376,7 +1382,8 @@ int fla_sm100_state_exchange(const FlaArgs* a, int which, const FlaExchange* x) 
   int rc = check_common(a, &dev);
   if (rc) return rc;
   if (x == nullptr || x->world < 1 || x->world > FLA_MAX_RANKS || x->rank < 0 ||
-      x->rank >= x->world || x->epoch == 0 || (which != 0 && which != 1))
+      x->rank >= x->world || (x->epoch == 0 && x->epoch_counter == nullptr) ||
+      (which != 0 && which != 1))
     return FLA_ERR_INVALID;
   for (int d = 0; d < x->world; ++d)
     if (x->inbox[d] == nullptr || x->flags[d] == nullptr) return FLA_ERR_INVALID;
@@ -1432,6 +1439,7 @@ int fla_sm100_state_exchange(const FlaArgs* a, int which, const FlaExchange* x) 
   xp.remote_out = x->remote_out;
   xp.inclusive_out = x->inclusive_out;
   xp.status = a->status;
+  xp.epoch_counter = x->epoch_counter;
   // Blocks per head: few enough that all blocks of all heads are resident together (four per SM),
   // but at most 16 elements per thread. The same on every rank (it indexes the flags).
   const int elems = da * dc;
@@ -1440,6 +1448,10 @@ int fla_sm100_state_exchange(const FlaArgs* a, int which, const FlaExchange* x) 
   bx = std::max(bx, (full + 15) / 16);
   fla_state_exchange_kernel<<<dim3(bx, bh, 1), 256, 0, stream>>>(xp);
   ++g_last_launches;
+  if (x->epoch_counter != nullptr) {
+    fla_exchange_bump_kernel<<<1, 1, 0, stream>>>(x->epoch_counter);
+    ++g_last_launches;
+  }
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) FLA_LOG_FAILURE("launch of fla_state_exchange_kernel failed: %s", cudaGetErrorString(e));
   return e == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;

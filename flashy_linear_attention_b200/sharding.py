@@ -153,7 +153,10 @@ class PeerStateExchange:
                             raise RuntimeError(f"flashlinear: mapping rank {r}'s exchange buffer: {_lib.strerror(rc)}")
                         self._opened.append(ptr.value)
                         dst[r] = ptr.value
-                self._sets.append({"inbox": inbox_ptrs, "flags": flag_ptrs, "epoch": 0})
+                # the exchange count lives on the device (one word per buffer set), so that calls
+                # carry no argument that changes between launches and can be replayed from a CUDA graph
+                counter = torch.zeros(1, dtype=torch.int32, device=device)
+                self._sets.append({"inbox": inbox_ptrs, "flags": flag_ptrs, "counter": counter})
         dist.barrier(group=group)
 
     def close(self) -> None:
@@ -181,7 +184,6 @@ class PeerStateExchange:
             raise ValueError("PeerStateExchange was created for another shape")
         lib = _lib.load()
         bset = self._sets[1 if reverse else 0]
-        bset["epoch"] += 1
         bv, cv = ops._kernel_view(b), ops._kernel_view(c)
         remote = torch.empty(B * H, db, dc, dtype=torch.float32, device=b.device)
         inclusive = torch.empty_like(remote)
@@ -191,7 +193,8 @@ class PeerStateExchange:
         a.k, a.v = ops._desc(bv), ops._desc(cv)
         a.segments = segments
         x = FlaExchange()
-        x.rank, x.world, x.reverse, x.epoch = self.rank, self.world, 1 if reverse else 0, bset["epoch"]
+        x.rank, x.world, x.reverse, x.epoch = self.rank, self.world, 1 if reverse else 0, 0
+        x.epoch_counter = bset["counter"].data_ptr()
         for r in range(self.world):
             x.inbox[r] = bset["inbox"][r]
             x.flags[r] = bset["flags"][r]

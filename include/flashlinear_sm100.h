@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define FLA_ABI_VERSION 7
+#define FLA_ABI_VERSION 8
 
 enum {
   FLA_OK = 0,
@@ -138,6 +138,10 @@ int fla_sm100_state(const FlaArgs* args, int which);
  * PROCESS (peer-mapped device memory, e.g. opened from CUDA IPC handles); inbox[rank] / flags[rank]
  * are this rank's own. Sizes: fla_sm100_exchange_bytes(). Both must be zero before the first use.
  * `epoch` starts at 1 and increases by 1 with every exchange on these buffers, on all ranks alike.
+ * Alternatively the count lives on the device: with `epoch_counter` set (a zero-initialised device
+ * word per buffer set, the same on every rank) the kernel uses *epoch_counter + 1 and a one-thread
+ * kernel behind it stores that value back; `epoch` is then ignored and the call has no argument
+ * that changes between launches, so it can be captured in a CUDA graph and replayed.
  * All ranks must make the same sequence of calls. A peer that never shows up makes the wait run
  * out after about 0.4 s: bit 1 of *status is set and the call's results are invalid. */
 #define FLA_MAX_RANKS 8
@@ -149,6 +153,7 @@ typedef struct FlaExchange {
   uint32_t* flags[FLA_MAX_RANKS];
   float* remote_out;    /* optional, fp32 [batch*heads, dk, dv] */
   float* inclusive_out; /* optional, fp32 [batch*heads, dk, dv] */
+  uint32_t* epoch_counter; /* optional device word, see above */
 } FlaExchange;
 /* Bytes of one rank's inbox (*inbox_bytes) and flag array (*flag_bytes) for these shapes. */
 int fla_sm100_exchange_bytes(const FlaArgs* args, int world, size_t* inbox_bytes, size_t* flag_bytes);

@@ -70,6 +70,18 @@ def _worker(rank, world, port, mode):
                 out = PeerShardedLinearAttention.apply(ql, kl, vl, ex)
                 out.backward(dy[:, :, lo:hi].contiguous())
             torch.cuda.synchronize()
+            # the same exchange replayed from a CUDA graph (its exchange count lives on the device)
+            from flashy_linear_attention_b200.graphs import capture_step
+
+            def fwd_only():
+                ws, _, _ = ex.state_and_exchange(kl.detach(), vl.detach(), reverse=False)
+                return ops.causal_dot_product_fwd(ql.detach(), kl.detach(), vl.detach(), segment_workspace=ws)
+
+            replay = capture_step(fwd_only)
+            for _ in range(3):
+                graphed = replay()
+            torch.cuda.synchronize()
+            assert torch.equal(graphed, out.detach()), (rank, "graph replay differs from the eager call")
             ex.close()
         want = (full[:, :, lo:hi], qf.grad[:, :, lo:hi], kf.grad[:, :, lo:hi], vf.grad[:, :, lo:hi])
     else:
