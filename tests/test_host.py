@@ -65,6 +65,11 @@ def test_invalid_arguments_are_rejected_without_a_gpu():
     assert need >= 2 * 4 * 128 * 128 * 4
     a.segments = 1
     assert lib.fla_sm100_workspace_bytes(ctypes.byref(a), 0) == 0
+    # more (batch, head) pairs than a grid dimension holds: refused before any device work
+    big = FlaArgs()
+    big.batch, big.heads, big.seqlen, big.dk, big.dv = 1024, 64, 128, 64, 64
+    assert lib.fla_sm100_fwd(ctypes.byref(big)) == -2
+    assert lib.fla_sm100_bwd(ctypes.byref(big)) == -2
     # the wide (SmallVHD) shapes never split the sequence: no scratch, one segment
     a.dk, a.dv, a.segments = 273, 64, 0
     assert lib.fla_sm100_workspace_bytes(ctypes.byref(a), 0) == 0

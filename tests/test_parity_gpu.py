@@ -649,3 +649,18 @@ def test_cuda_graph_capture_replays_the_same_results(shape):
     ops.check_status(DEV)
     for a, b in zip(got, want):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 100, 64, 64), (2, 1, 1, 128, 128), (1, 1, 129, 128, 128), (1, 2, 250, 96, 32),
+                                   (1, 1, 200, 273, 64)], ids=lambda s: "x".join(map(str, s)))
+def test_ragged_sequence_lengths_below_the_wrappers_granularity(shape):
+    """The reference wrappers insist on multiples of 64 tokens (linear_attn_kernels.py:323-325); the
+    kernels themselves take any length: out-of-range tokens of the last chunk read as zero and are
+    not written."""
+    B, H, N, dk, dv = shape
+    rng = np.random.default_rng(N)
+    q = orc.bf16_round((orc.elu_plus_one(rng.standard_normal((B, H, N, dk))) / np.sqrt(dk / 64)).astype(np.float32))
+    k = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, dk))).astype(np.float32))
+    v = orc.bf16_round(rng.standard_normal((B, H, N, dv)).astype(np.float32))
+    dy = orc.bf16_round(rng.standard_normal((B, H, N, dv)).astype(np.float32))
+    _run_and_check(q, k, v, dy)
