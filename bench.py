@@ -38,6 +38,7 @@ WORKLOADS = {
     "cfg3_half": (4, 32, 4096, 128, 128),   # cfg3 at half the sequence length (1 GB resident)
     "cfg4": (8, 16, 2048, 273, 64),  # LinearAttentionSmallVHD, 2nd-order Taylor features of 16 dims
     "cfg5": (1, 32, 65536, 128, 128),
+    "cfg5_quarter": (1, 32, 16384, 128, 128),  # cfg5's head count at N=16384 (1 GB resident): for ncu captures
 }
 METRIC = "fwd+bwd Mtokens/s, N=8K D=128 bf16, 1/2/4/8 B200; % tensor/HBM roofline"
 UNIT = "Mtokens/s"
