@@ -153,36 +153,66 @@ struct ScanParams {
   int have_last;  // the last segment's sum is present (needed only for ext_final)
 };
 
-__global__ void fla_state_scan_kernel(const ScanParams sp) {
+// Block = 32 x 32 threads on a 32 x 32 tile of the state: thread (tx, ty) scans element
+// (row = row0 + tx, col = col0 + ty), so the scratch ([col][row]) is read and written along tx.
+// The caller-layout arrays ([row][col], or the scratch layout when ext_trans) are touched through
+// a shared-memory transpose, along tx as well: whole 128-byte segments instead of one word per line.
+__global__ void __launch_bounds__(1024) fla_state_scan_kernel(const ScanParams sp) {
+  __shared__ float tile[32][33];
   const ScanProblem pr = sp.prob[blockIdx.z];
   const int bh = blockIdx.y;
   const int elems = sp.rows * sp.cols;
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= elems) return;
-  const int col = e / sp.rows, row = e % sp.rows;  // scratch layout [col][row]
-  const size_t ext_idx = static_cast<size_t>(bh) * elems +
-                         (pr.ext_trans ? static_cast<size_t>(e) : static_cast<size_t>(row) * sp.cols + col);
-  float run = pr.ext_init ? pr.ext_init[ext_idx] : 0.f;
-  float* __restrict__ base = pr.ws + static_cast<size_t>(bh) * sp.nseg * elems + e;
-  const int npresent = sp.have_last ? sp.nseg : sp.nseg - 1;  // segments whose sum was written
-  // Batches of 8 segments: all loads of a batch are issued before the dependent stores.
-  for (int g0 = 0; g0 < sp.nseg; g0 += 8) {
-    float local[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int g = g0 + j;
-      local[j] = (g < npresent) ? __ldcg(base + static_cast<size_t>(g) * elems) : 0.f;
+  const int tiles_r = (sp.rows + 31) / 32;
+  const int row0 = (blockIdx.x % tiles_r) * 32, col0 = (blockIdx.x / tiles_r) * 32;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int row = row0 + tx, col = col0 + ty;
+  const bool valid = row < sp.rows && col < sp.cols;
+  const size_t ext_base = static_cast<size_t>(bh) * elems;
+  // element this thread moves for the caller-layout arrays: (row0 + ty, col0 + tx)
+  const int trow = row0 + ty, tcol = col0 + tx;
+  const bool tvalid = trow < sp.rows && tcol < sp.cols;
+  float run = 0.f;
+  if (pr.ext_init != nullptr) {
+    if (pr.ext_trans) {
+      if (valid) run = pr.ext_init[ext_base + static_cast<size_t>(col) * sp.rows + row];
+    } else {
+      tile[ty][tx] = tvalid ? pr.ext_init[ext_base + static_cast<size_t>(trow) * sp.cols + tcol] : 0.f;
+      __syncthreads();
+      run = tile[tx][ty];
+      __syncthreads();
     }
+  }
+  if (valid) {
+    float* __restrict__ base = pr.ws + static_cast<size_t>(bh) * sp.nseg * elems +
+                               static_cast<size_t>(col) * sp.rows + row;
+    const int npresent = sp.have_last ? sp.nseg : sp.nseg - 1;  // segments whose sum was written
+    // Batches of 8 segments: all loads of a batch are issued before the dependent stores.
+    for (int g0 = 0; g0 < sp.nseg; g0 += 8) {
+      float local[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int g = g0 + j;
-      if (g < sp.nseg) {
-        base[static_cast<size_t>(g) * elems] = run;
-        run += local[j];
+      for (int j = 0; j < 8; ++j) {
+        const int g = g0 + j;
+        local[j] = (g < npresent) ? __ldcg(base + static_cast<size_t>(g) * elems) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int g = g0 + j;
+        if (g < sp.nseg) {
+          base[static_cast<size_t>(g) * elems] = run;
+          run += local[j];
+        }
       }
     }
   }
-  if (pr.ext_final) pr.ext_final[ext_idx] = run;
+  if (pr.ext_final != nullptr) {
+    if (pr.ext_trans) {
+      if (valid) pr.ext_final[ext_base + static_cast<size_t>(col) * sp.rows + row] = run;
+    } else {
+      tile[ty][tx] = run;
+      __syncthreads();
+      if (tvalid) pr.ext_final[ext_base + static_cast<size_t>(trow) * sp.cols + tcol] = tile[tx][ty];
+    }
+  }
 }
 
 // ---------------------------------------------------------------- scan fused with the exchange
@@ -584,9 +614,8 @@ int run_products(const Product* prods, int nprob, int B, int H, int N, int da, i
   sp.bh_count = bh;
   sp.have_last = want_final ? 1 : 0;
   {
-    const int elems = da * dc;
-    dim3 grid((elems + 255) / 256, bh, nprob);
-    fla_state_scan_kernel<<<grid, 256, 0, stream>>>(sp);
+    dim3 grid(((da + 31) / 32) * ((dc + 31) / 32), bh, nprob);
+    fla_state_scan_kernel<<<grid, dim3(32, 32, 1), 0, stream>>>(sp);
     ++g_last_launches;
     if (cudaGetLastError() != cudaSuccess) return FLA_ERR_CUDA;
   }
@@ -643,8 +672,7 @@ int run_state(const Operand& bop, const Operand& cop, int B, int H, int N, int d
   sp.cols = dc;
   sp.bh_count = bh;
   sp.have_last = 1;
-  const int elems = da * dc;
-  fla_state_scan_kernel<<<dim3((elems + 255) / 256, bh, 1), 256, 0, stream>>>(sp);
+  fla_state_scan_kernel<<<dim3(((da + 31) / 32) * ((dc + 31) / 32), bh, 1), dim3(32, 32, 1), 0, stream>>>(sp);
   ++g_last_launches;
   return cudaGetLastError() == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
 }
