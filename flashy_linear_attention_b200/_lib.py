@@ -11,7 +11,9 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libflashlinear_sm100.so")
 
-FLA_ABI_VERSION = 8
+FLA_ABI_VERSION = 9
+FLA_DEBUG_WITHHOLD_FIRST_TILE = 1
+FLA_DEBUG_NO_FUSED_SEGMENTS = 2
 FLA_MAX_RANKS = 8
 
 
@@ -50,6 +52,10 @@ class FlaArgs(ctypes.Structure):
         ("workspace_bytes", ctypes.c_size_t),
         ("status", ctypes.c_void_p),
         ("stream", ctypes.c_void_p),
+        ("seg_states", ctypes.c_void_p),
+        ("seg_states_bytes", ctypes.c_size_t),
+        ("wait_limit_us", ctypes.c_uint32),
+        ("debug_flags", ctypes.c_uint32),
     ]
 
 
@@ -64,6 +70,7 @@ class FlaExchange(ctypes.Structure):
         ("remote_out", ctypes.c_void_p),
         ("inclusive_out", ctypes.c_void_p),
         ("epoch_counter", ctypes.c_void_p),
+        ("wait_limit_us", ctypes.c_uint32),
     ]
 
 
@@ -72,6 +79,7 @@ EXPORTED_SYMBOLS = (
     "fla_sm100_strerror",
     "fla_sm100_workspace_bytes",
     "fla_sm100_auto_segments",
+    "fla_sm100_seg_states_bytes",
     "fla_sm100_fwd",
     "fla_sm100_bwd",
     "fla_sm100_state",
@@ -118,6 +126,8 @@ def load() -> ctypes.CDLL:
     lib.fla_sm100_workspace_bytes.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_int]
     lib.fla_sm100_auto_segments.restype = ctypes.c_int
     lib.fla_sm100_auto_segments.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_int]
+    lib.fla_sm100_seg_states_bytes.restype = ctypes.c_size_t
+    lib.fla_sm100_seg_states_bytes.argtypes = [ctypes.POINTER(FlaArgs)]
     lib.fla_sm100_fwd.restype = ctypes.c_int
     lib.fla_sm100_fwd.argtypes = [ctypes.POINTER(FlaArgs)]
     lib.fla_sm100_bwd.restype = ctypes.c_int

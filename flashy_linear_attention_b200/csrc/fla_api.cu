@@ -55,6 +55,11 @@ EncodeTiledFn get_encode_fn() {
 }
 
 thread_local int g_last_launches = 0;
+// Bounded-wait limit (units of 1024 SM cycles, 0 = default) and the wait-timeout test hook of the
+// call in progress on this thread; check_common() sets them from FlaArgs.
+thread_local unsigned g_wait_limit_kcycles = 0;
+thread_local int g_debug_withhold = 0;
+thread_local int g_no_fused = 0;  // FLA_DEBUG_NO_FUSED_SEGMENTS: keep the three-launch segmented path
 
 // FLA_DEBUG=1 in the environment: failed CUDA calls are described on stderr.
 bool debug_enabled() {
@@ -72,10 +77,6 @@ bool debug_enabled() {
       fprintf(stderr, "\n");                  \
     }                                         \
   } while (0)
-#ifdef FLA_TRACE
-long long* g_trace = nullptr;  // tracing build only: timeline buffer handed to launches of g_trace_mode
-int g_trace_mode = 0;
-#endif
 
 struct Operand {
   const void* ptr;
@@ -134,6 +135,14 @@ struct Product {
   const float* ext_init;  // caller's running state, or null
   float* ext_final;
   int ext_trans;  // the caller's state arrays hold the transpose of the product's [da][dc] state
+  // Fused segmented launch only. With bound_base set, segment 0 starts from ext_init and segment
+  // g >= 1 from the stored boundary state (bound_slot0 - g * bound_step) of bound_base
+  // ([bh][bound_stride][da*dc], layout flag bound_trans relative to this product's state) instead
+  // of from the partial sums of the launch. bound_out: segments g >= 1 store the state they start
+  // from ([bh][segments - 1][da*dc], scratch layout) for a later call to use as bound_base.
+  const float* bound_base = nullptr;
+  int bound_stride = 0, bound_slot0 = 0, bound_step = 0, bound_trans = 0;
+  float* bound_out = nullptr;
 };
 
 // ---------------------------------------------------------------- segment state scan
@@ -232,6 +241,7 @@ struct ExchangeParams {
   float* inclusive_out;
   int* status;
   const unsigned* epoch_counter;  // device-side count (epoch = *epoch_counter + 1), or null
+  unsigned long long wait_limit_ns;  // how long a block waits for a peer's flag
 };
 
 // Stores the epoch an exchange kernel just used back into its device-side counter.
@@ -242,12 +252,13 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
 __device__ __forceinline__ void st_relaxed_sys(unsigned* p, unsigned v) {
   asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
 }
 
 // Every thread handles the elements e0, e0 + stride, ... of one head (stride = threads of the
@@ -294,27 +305,32 @@ __global__ void fla_state_exchange_kernel(const ExchangeParams xp) {
   if (static_cast<int>(threadIdx.x) < xp.world && static_cast<int>(threadIdx.x) != xp.rank) {
     const unsigned* f = xp.flags[xp.rank] +
                         (static_cast<size_t>(parity) * xp.world + threadIdx.x) * nblocks + block_id;
-    const long long t0 = clock64();
+    const unsigned long long t0 = globaltimer_ns();
+    unsigned spins = 0;
     while (ld_acquire_sys(f) != epoch) {
-      if (clock64() - t0 > fla::ptx::kWaitLimitCycles) {
+      if ((++spins & 15u) == 0u && globaltimer_ns() - t0 > xp.wait_limit_ns) {
         timed_out = 1;
         break;
       }
     }
   }
   __syncthreads();
-  if (timed_out) {
-    if (threadIdx.x == 0 && xp.status != nullptr) atomicOr(xp.status, 2);
-    return;
-  }
+  const bool failed = timed_out != 0;
+  if (failed && threadIdx.x == 0 && xp.status != nullptr) atomicOr(xp.status, 2);
+  // A wait that ran out must not leave plausible numbers behind: everything this block would have
+  // produced becomes NaN, so the outputs of the passes built on it are NaN too and the failure shows
+  // even where nobody reads the status word.
+  const float poison = __int_as_float(0x7fc00000);
   const int lo = xp.reverse ? xp.rank + 1 : 0;
   const int hi = xp.reverse ? xp.world : xp.rank;
   for (int e = e0; e < elems; e += stride) {
     // 4. totals of the ranks before (after) this one, from this GPU's own inbox
-    float remote = 0.f;
-    for (int s = lo; s < hi; ++s)
-      remote += __ldcg(xp.inbox[xp.rank] + (static_cast<size_t>(parity) * xp.world + s) * state_elems +
-                       static_cast<size_t>(bh) * elems + e);
+    float remote = failed ? poison : 0.f;
+    if (!failed) {
+      for (int s = lo; s < hi; ++s)
+        remote += __ldcg(xp.inbox[xp.rank] + (static_cast<size_t>(parity) * xp.world + s) * state_elems +
+                         static_cast<size_t>(bh) * elems + e);
+    }
     // 5. segment prefixes on top of it
     float run = remote;
     for (int g = 0; g < xp.nseg; ++g) {
@@ -411,6 +427,7 @@ __global__ void fla_unpad_rows_kernel(const unsigned short* __restrict__ src,
 struct DeviceInfo {
   int sm_count;
   int cc_major;
+  int clock_khz;  // nominal SM clock, converts FlaArgs::wait_limit_us to cycles
   bool attr_set[2];
 };
 
@@ -435,6 +452,8 @@ int device_info(DeviceInfo** out) {
       DeviceInfo& d = infos[dev];
       d.sm_count = 148;
       d.cc_major = 0;
+      d.clock_khz = 1965000;
+      cudaDeviceGetAttribute(&d.clock_khz, cudaDevAttrClockRate, dev);
       cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
       cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
       bool ok = true;
@@ -478,6 +497,12 @@ int pick_template(int da, int dc) {
   return 0;
 }
 
+int current_sm_count_early() {
+  int sm = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev);
+  return sm;
+}
+
 int auto_segments(int nprob, int bh, int nchunks, int sm_count) {
   const long ctas = static_cast<long>(nprob) * bh;
   if (ctas * 4 >= static_cast<long>(sm_count) * 3) return 1;  // already >= 75 % of the SMs
@@ -498,12 +523,62 @@ size_t segment_ws_bytes(int nprob, int bh, int nseg, int rows, int cols) {
   return static_cast<size_t>(nprob) * bh * nseg * rows * cols * sizeof(float);
 }
 
+struct SegPlan {
+  int nseg;
+  int seg_chunks;
+};
+
+SegPlan make_plan(int want, int nchunks) {
+  if (want > nchunks) want = nchunks;
+  if (want < 1) want = 1;
+  SegPlan p;
+  p.seg_chunks = (nchunks + want - 1) / want;
+  p.nseg = (nchunks + p.seg_chunks - 1) / p.seg_chunks;
+  return p;
+}
+
+// Segments of a forward call (one product per head).
+SegPlan forward_plan(const FlaArgs* a, int sm_count) {
+  const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
+  const int want = a->segments > 0 ? a->segments : auto_segments(1, a->batch * a->heads, nchunks, sm_count);
+  return make_plan(want, nchunks);
+}
+
+// Segments of a backward call (three products per head) whose boundaries are boundaries of the
+// forward plan `f`, so that the states the forward stored at its boundaries can start dQ's
+// segments. nseg = 1 when no such plan exists or the backward would not be split anyway.
+SegPlan backward_aligned_plan(const FlaArgs* a, int sm_count, const SegPlan& f) {
+  const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
+  const int bh = a->batch * a->heads;
+  const SegPlan none = {1, nchunks};
+  const SegPlan base = make_plan(auto_segments(3, bh, nchunks, sm_count), nchunks);
+  if (base.nseg <= 1 || f.nseg <= 1 || nchunks % f.seg_chunks != 0) return none;
+  SegPlan b;
+  b.seg_chunks = (base.seg_chunks + f.seg_chunks - 1) / f.seg_chunks * f.seg_chunks;
+  b.nseg = (nchunks + b.seg_chunks - 1) / b.seg_chunks;
+  if (b.nseg <= 1 || 3l * b.nseg * bh > sm_count) return none;
+  return b;
+}
+
+// Bytes of the boundary states a fused forward stores for a fused backward, or 0 when the pair of
+// calls does not run that way for these shapes.
+size_t seg_states_bytes(const FlaArgs* a, int sm_count, SegPlan* fwd_out, SegPlan* bwd_out) {
+  if (a->dk != a->dv || a->dk > 128 || g_no_fused) return 0;
+  const int bh = a->batch * a->heads;
+  const SegPlan f = forward_plan(a, sm_count);
+  if (f.nseg <= 1 || static_cast<long>(f.nseg) * bh > sm_count) return 0;
+  const SegPlan b = backward_aligned_plan(a, sm_count, f);
+  if (b.nseg <= 1) return 0;
+  if (fwd_out) *fwd_out = f;
+  if (bwd_out) *bwd_out = b;
+  return static_cast<size_t>(f.nseg - 1) * bh * a->dk * a->dv * sizeof(float);
+}
+
 template <int D>
 int launch_kernel(const KernelParams& kp_in, dim3 grid, cudaStream_t stream) {
   KernelParams kp = kp_in;
-#ifdef FLA_TRACE
-  kp.trace = (kp.mode == g_trace_mode) ? g_trace : nullptr;
-#endif
+  kp.wait_limit_kcycles = g_wait_limit_kcycles;
+  kp.debug_withhold = g_debug_withhold;
   fla::fla_chunk_kernel<D, D><<<grid, fla::kThreads, fla::Cfg<D, D>::SMEM_BYTES, stream>>>(kp);
   ++g_last_launches;
   const cudaError_t e = cudaGetLastError();
@@ -519,11 +594,49 @@ int launch_template(int tmpl, const KernelParams& kp, dim3 grid, cudaStream_t st
   return FLA_ERR_UNSUPPORTED;
 }
 
+// Cooperative launch (all CTAs resident at once, or the launch fails) of the fused segmented form.
+template <int D>
+int launch_fused_kernel(const KernelParams& kp_in, dim3 grid, cudaStream_t stream) {
+  static std::atomic<unsigned> next_slot{0};
+  KernelParams kp = kp_in;
+  kp.wait_limit_kcycles = g_wait_limit_kcycles;
+  kp.debug_withhold = g_debug_withhold;
+  kp.bar_slot = next_slot.fetch_add(1, std::memory_order_relaxed) % fla::kGridBarSlots;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(fla::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = fla::Cfg<D, D>::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  memset(&attr, 0, sizeof(attr));
+  attr.id = cudaLaunchAttributeCooperative;
+  attr.val.cooperative = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, fla::fla_chunk_kernel<D, D>, kp);
+  ++g_last_launches;
+  if (e != cudaSuccess) {
+    FLA_LOG_FAILURE("cooperative launch of fla_chunk_kernel<%d> grid (%u,%u,%u) failed: %s", D, grid.x,
+                    grid.y, grid.z, cudaGetErrorString(e));
+    (void)cudaGetLastError();
+  }
+  return e == cudaSuccess ? FLA_OK : FLA_ERR_CUDA;
+}
+
+int launch_fused(int tmpl, const KernelParams& kp, dim3 grid, cudaStream_t stream) {
+  if (tmpl == 64) return launch_fused_kernel<64>(kp, grid, stream);
+  if (tmpl == 128) return launch_fused_kernel<128>(kp, grid, stream);
+  return FLA_ERR_UNSUPPORTED;
+}
+
 // Runs `nprob` products that share shapes (da, dc) in one grid (plus, with segments, a state pass
 // and a scan before it).
+// `seg_chunks_in` > 0 fixes the segment length (in chunks) instead of deriving it from `segments`.
 int run_products(const Product* prods, int nprob, int B, int H, int N, int da, int dc,
                  int segments, void* workspace, size_t workspace_bytes, int32_t* status,
-                 cudaStream_t stream, const DeviceInfo& dev, bool states_ready = false) {
+                 cudaStream_t stream, const DeviceInfo& dev, bool states_ready = false,
+                 int seg_chunks_in = 0) {
   const int tmpl = pick_template(da, dc);
   if (tmpl == 0) return FLA_ERR_UNSUPPORTED;
   const int bh = B * H;
@@ -531,7 +644,7 @@ int run_products(const Product* prods, int nprob, int B, int H, int N, int da, i
   int nseg = segments;
   if (nseg <= 0) nseg = auto_segments(nprob, bh, nchunks, dev.sm_count);
   if (nseg > nchunks) nseg = nchunks;
-  const int seg_chunks = (nchunks + nseg - 1) / nseg;
+  const int seg_chunks = seg_chunks_in > 0 ? seg_chunks_in : (nchunks + nseg - 1) / nseg;
   nseg = (nchunks + seg_chunks - 1) / seg_chunks;
   const size_t ws_per_prob = static_cast<size_t>(bh) * nseg * da * dc;
   if (nseg > 1) {
@@ -591,6 +704,68 @@ int run_products(const Product* prods, int nprob, int B, int H, int N, int da, i
   }
 
   float* ws = static_cast<float*>(workspace);
+  // The fused form sums ONE state per (head, segment). Products that start from the partial sums
+  // must therefore all carry that state or its transpose (dV and dK: q^T dO and dO^T q) and walk
+  // the sequence in the same direction; a product with another state (dQ: v^T k) can only ride
+  // along when its starting states come from stored boundary states.
+  bool fusable = !g_no_fused && static_cast<long>(nprob) * nseg * bh <= dev.sm_count;
+  {
+    const Product* first = nullptr;
+    for (int i = 0; i < nprob && fusable; ++i) {
+      const Product& pd = prods[i];
+      if (pd.bound_base != nullptr) continue;
+      if (first == nullptr) {
+        first = &pd;
+        continue;
+      }
+      const bool same = pd.b.ptr == first->b.ptr && pd.c.ptr == first->c.ptr && pd.ext_trans == first->ext_trans;
+      const bool swapped = pd.b.ptr == first->c.ptr && pd.c.ptr == first->b.ptr && pd.ext_trans != first->ext_trans;
+      const bool same_dir = ((pd.flags ^ first->flags) & fla::kFlagDescending) == 0;
+      if (!(same || swapped) || !same_dir || da != dc) fusable = false;
+    }
+    if (first == nullptr) fusable = false;
+  }
+  if (fusable) {
+    // Everything fits the GPU at once: ONE cooperative launch in which every CTA sums its share of
+    // its segment (phase A), all CTAs meet at a grid barrier, and each then starts the attention
+    // loop from the sum of the partials of the earlier segments. The three-launch form below pays
+    // the pipeline fill and drain of a launch three times and reads b, c once more from HBM.
+    int pre = 0;
+    for (int i = 0; i < nprob; ++i) {
+      Problem& pr = kp.prob[i];
+      const Product& pd = prods[i];
+      pr.s_init = nullptr;
+      pr.s_add = pd.ext_init;
+      pr.add_trans = pd.ext_trans;
+      pr.s_final = pd.ext_final;   // written by the last segment's CTA
+      pr.st_trans = pd.ext_trans;
+      if (pd.bound_base != nullptr) {
+        pr.init_kind = fla::kInitBound;
+        pr.init_base = pd.bound_base;
+        pr.init_trans = pd.bound_trans;
+        pr.init_stride = pd.bound_stride;
+        pr.bound_slot0 = pd.bound_slot0;
+        pr.bound_step = pd.bound_step;
+      } else {
+        pr.init_kind = fla::kInitParts;
+        pr.init_base = ws;
+        // The partials hold the state of problem `pre` in the scratch layout; a problem whose own
+        // state is the transpose of that one (dK beside dV) reads them the other way round.
+        pre = i;
+      }
+      pr.bound_out = pd.bound_out;
+    }
+    // `pre`: the (last) problem that starts from partial sums; its b, c operands and direction
+    // define phase A. Problems with the transposed state read the partials transposed.
+    for (int i = 0; i < nprob; ++i)
+      if (kp.prob[i].init_kind == fla::kInitParts)
+        kp.prob[i].init_trans = (prods[i].ext_trans == prods[pre].ext_trans) ? 1 : 0;
+    kp.mode = 0;
+    kp.fused = 1;
+    kp.pre_prob = pre;
+    kp.part_out = ws;
+    return launch_fused(tmpl, kp, dim3(nprob, nseg, bh), stream);
+  }
   // Pass A: per-segment sums of b^T c into the workspace (the last segment only when a final
   // state is wanted), exclusive scan over segments, then pass B with per-segment initial states.
   ScanParams sp;
@@ -704,6 +879,8 @@ int run_wide_a(const Product& pd, int B, int H, int N, int da, int dc, int32_t* 
   wp.nchunks = (N + fla::kWideChunk - 1) / fla::kWideChunk;
   wp.da = da;
   wp.status = status;
+  wp.wait_limit_kcycles = g_wait_limit_kcycles;
+  wp.debug_withhold = g_debug_withhold;
   const dim3 grid(1, 1, B * H);
   if (da <= 256)
     fla::fla_wide_kernel<2><<<grid, fla::kWideThreads, fla::WideCfg<2>::SMEM_BYTES, stream>>>(wp);
@@ -752,6 +929,14 @@ int check_common(const FlaArgs* a, DeviceInfo** dev) {
   if (rc) return rc;
   if ((*dev)->cc_major != 10) return FLA_ERR_DEVICE;
   if (!(*dev)->attr_set[0]) return FLA_ERR_CUDA;
+  g_wait_limit_kcycles = 0;
+  if (a->wait_limit_us != 0) {
+    const unsigned long long cycles =
+        static_cast<unsigned long long>(a->wait_limit_us) * (*dev)->clock_khz / 1000ull;
+    g_wait_limit_kcycles = static_cast<unsigned>(std::min<unsigned long long>((cycles >> 10) + 1, 0x7fffffffull));
+  }
+  g_debug_withhold = (a->debug_flags & FLA_DEBUG_WITHHOLD_FIRST_TILE) ? 1 : 0;
+  g_no_fused = (a->debug_flags & FLA_DEBUG_NO_FUSED_SEGMENTS) ? 1 : 0;
   return FLA_OK;
 }
 
@@ -797,13 +982,6 @@ extern "C" {
 
 int fla_sm100_abi_version(void) { return FLA_ABI_VERSION; }
 
-#ifdef FLA_TRACE
-void fla_sm100_set_trace(long long* buf, int mode) {
-  g_trace = buf;
-  g_trace_mode = mode;
-}
-#endif
-
 const char* fla_sm100_strerror(int code) {
   switch (code) {
     case FLA_OK: return "ok";
@@ -844,6 +1022,16 @@ size_t fla_sm100_workspace_bytes(const FlaArgs* a, int pass) {
   return segment_ws_bytes(pass == 1 ? 3 : 1, a->batch * a->heads, nseg, a->dk, a->dv) + 1024;
 }
 
+size_t fla_sm100_seg_states_bytes(const FlaArgs* a) {
+  if (a == nullptr || a->batch <= 0 || a->heads <= 0 || a->seqlen <= 0) return 0;
+  if (a->segment_states_ready) return 0;
+  const int saved = g_no_fused;
+  g_no_fused = (a->debug_flags & FLA_DEBUG_NO_FUSED_SEGMENTS) ? 1 : 0;
+  const size_t n = seg_states_bytes(a, current_sm_count_early(), nullptr, nullptr);
+  g_no_fused = saved;
+  return n;
+}
+
 int fla_sm100_fwd(const FlaArgs* a) {
   DeviceInfo* dev = nullptr;
   g_last_launches = 0;
@@ -861,6 +1049,13 @@ int fla_sm100_fwd(const FlaArgs* a) {
   if (is_wide_a(a->dk, a->dv))
     return run_wide_a(p, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->status,
                       static_cast<cudaStream_t>(a->stream));
+  if (a->seg_states != nullptr && a->segment_states_ready == 0) {
+    const size_t need = seg_states_bytes(a, dev->sm_count, nullptr, nullptr);
+    if (need > 0) {
+      if (a->seg_states_bytes < need) return FLA_ERR_WORKSPACE;
+      p.bound_out = static_cast<float*>(a->seg_states);
+    }
+  }
   return run_products(&p, 1, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->segments,
                       a->workspace, a->workspace_bytes, a->status,
                       static_cast<cudaStream_t>(a->stream), *dev, a->segment_states_ready != 0);
@@ -914,6 +1109,29 @@ int fla_sm100_bwd(const FlaArgs* a) {
     return rc;
   }
   const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
+  if (a->seg_states != nullptr && a->s_last != nullptr) {
+    // Few heads: the forward ran as one fused segmented launch and stored the state at each of
+    // its segment boundaries. The backward is split at a subset of those boundaries; dQ walks every
+    // segment end-to-start from the stored state at the segment's end (total minus suffix, as in
+    // the unsegmented case), dV and dK start from the partial sums of q^T dO that the same launch
+    // forms first. One launch, and the three products of a (head, segment) stream the same chunks.
+    SegPlan f, bp;
+    const size_t need = seg_states_bytes(a, dev->sm_count, &f, &bp);
+    if (need > 0) {
+      if (a->seg_states_bytes < need) return FLA_ERR_WORKSPACE;
+      pq.flags = fla::kFlagDescending | fla::kFlagTotalMinusSuffix;
+      if (a->s_init == nullptr) pq.flags |= fla::kFlagFirstChunkExact;
+      pq.ext_init = a->s_last;  // segment 0 of the descending walk: the end of the sequence
+      pq.bound_base = static_cast<const float*>(a->seg_states);
+      pq.bound_trans = 0;       // stored as S in the scratch layout = S^T row-major
+      pq.bound_stride = f.nseg - 1;
+      pq.bound_slot0 = nchunks / f.seg_chunks - 1;
+      pq.bound_step = bp.seg_chunks / f.seg_chunks;
+      Product all[3] = {pq, pv, pk};
+      return run_products(all, 3, a->batch, a->heads, a->seqlen, a->dk, a->dv, bp.nseg, a->workspace,
+                          a->workspace_bytes, a->status, stream, *dev, false, bp.seg_chunks);
+    }
+  }
   int nseg = a->segments > 0 ? a->segments
                              : auto_segments(3, a->batch * a->heads, nchunks, dev->sm_count);
   if (nseg > nchunks) nseg = nchunks;
@@ -965,6 +1183,19 @@ int fla_sm100_fwd_static_scratch(const FlaArgs* a) {
   g_last_launches = 0;
   int rc = check_common(a, &dev);
   if (rc) return rc;
+  Product p;
+  p.a = operand(a->q, a->dk);
+  p.b = operand(a->k, a->dk);
+  p.c = operand(a->v, a->dv);
+  p.out = operand(a->o, a->dv);
+  p.flags = 0;
+  p.ext_init = a->s_init;
+  p.ext_final = a->s_final;
+  p.ext_trans = 0;
+  // q/k wider than 128 with a narrow v: that kernel never splits the sequence and uses no scratch
+  if (is_wide_a(a->dk, a->dv))
+    return run_wide_a(p, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->status,
+                      static_cast<cudaStream_t>(a->stream));
   // How much scratch this shape needs with the segment count the call will use.
   const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
   int nseg = a->segments > 0 ? a->segments
@@ -976,22 +1207,15 @@ int fla_sm100_fwd_static_scratch(const FlaArgs* a) {
   }
   const size_t need = segment_ws_bytes(1, a->batch * a->heads, nseg, a->dk, a->dv);
   if (need > static_cast<size_t>(FLA_STATIC_SCRATCH_BYTES)) return FLA_ERR_SCRATCH_LIMIT;
+  // The array's address is looked up only by calls that use it, so an unsegmented call never
+  // makes the symbol query (which is not allowed while a stream is being captured).
   void* scratch = nullptr;
-  if ((rc = static_scratch_address(&scratch)) != FLA_OK) return rc;
-  Product p;
-  p.a = operand(a->q, a->dk);
-  p.b = operand(a->k, a->dk);
-  p.c = operand(a->v, a->dv);
-  p.out = operand(a->o, a->dv);
-  p.flags = 0;
-  p.ext_init = a->s_init;
-  p.ext_final = a->s_final;
-  p.ext_trans = 0;
+  if (nseg > 1 && (rc = static_scratch_address(&scratch)) != FLA_OK) return rc;
   // Nothing in the scratch has to start at zero: every per-segment sum that the scan reads is
   // written by the state pass of this same call first.
   return run_products(&p, 1, a->batch, a->heads, a->seqlen, a->dk, a->dv, nseg, scratch,
-                      FLA_STATIC_SCRATCH_BYTES, a->status, static_cast<cudaStream_t>(a->stream),
-                      *dev);
+                      nseg > 1 ? FLA_STATIC_SCRATCH_BYTES : 0, a->status,
+                      static_cast<cudaStream_t>(a->stream), *dev);
 }
 
 int fla_sm100_taylor_dims(int d, int* features, int* padded) {
@@ -1468,12 +1692,16 @@ int fla_sm100_state_exchange(const FlaArgs* a, int which, const FlaExchange* x) 
   xp.inclusive_out = x->inclusive_out;
   xp.status = a->status;
   xp.epoch_counter = x->epoch_counter;
-  // Blocks per head: few enough that all blocks of all heads are resident together (four per SM),
-  // but at most 16 elements per thread. The same on every rank (it indexes the flags).
+  xp.wait_limit_ns = (x->wait_limit_us ? static_cast<unsigned long long>(x->wait_limit_us) : 400000ull) * 1000ull;
+  // Blocks per head: every block waits for its twin on the other GPUs, so all blocks of all heads
+  // must be resident together. At most four blocks per SM are used (others may share the GPU);
+  // threads loop over the elements their blocks do not cover. The count depends on the shapes
+  // only, so it is the same on every rank (it indexes the flags).
   const int elems = da * dc;
   const int full = (elems + 255) / 256;
-  int bx = std::min(full, std::max(1, 592 / bh));
-  bx = std::max(bx, (full + 15) / 16);
+  const int resident = 4 * 148;
+  if (bh > resident) return FLA_ERR_UNSUPPORTED;
+  const int bx = std::min(full, std::max(1, resident / bh));
   fla_state_exchange_kernel<<<dim3(bx, bh, 1), 256, 0, stream>>>(xp);
   ++g_last_launches;
   if (x->epoch_counter != nullptr) {

@@ -42,7 +42,21 @@ struct Problem {
   int n_tokens;            // sequence length
   int add_trans;           // layout of s_add: transposed like st_trans
   const float* s_add;      // optional [bh][st_rows][st_cols] fp32 added to s_init for every segment
+  // ---- fused segments only (KernelParams::fused): where the state a segment starts from comes from
+  int init_kind;           // kInitParts: s_add + the partial sums of all earlier segments;
+                           // kInitBound: segment 0 starts from s_add, segment g >= 1 from ONE stored
+                           // boundary state, slot bound_slot0 - g * bound_step of init_base
+  int init_trans;          // layout of the init_base arrays relative to this product's state
+  const float* init_base;  // kInitParts: [bh][segments * splits][rows*cols] (KernelParams::part_out);
+                           // kInitBound: [bh][init_stride][rows*cols]
+  int init_stride;         // kInitBound: boundary states per head
+  int bound_slot0, bound_step;
+  float* bound_out;        // optional: segment g >= 1 stores the state it starts from at slot g - 1 of
+                           // [bh][segments - 1][rows*cols], scratch layout (a later pass reads it back
+                           // through kInitBound)
 };
+constexpr int kInitParts = 0;
+constexpr int kInitBound = 1;
 
 // Problem::flags
 constexpr int kFlagDescending = 1;  // walk the chunks from the last token to the first
@@ -68,23 +82,28 @@ struct KernelParams {
   int st_cols;
   int skip_last_segment;  // mode 1: the last segment's sum is not needed
   int* status;     // device word, bit 0 set when a bounded wait ran out; may be null
-  long long* trace;  // timeline buffer of the tracing build (FLA_TRACE), else unused
+  unsigned wait_limit_kcycles;  // limit of one bounded wait in units of 1024 SM cycles; 0 = default
+  int debug_withhold;  // test hook: the producer skips the load of its first tile, so that the
+                       // consumers' bounded wait runs out and the status path is exercised
+  // ---- fused segments: ONE launch does what mode 1 + the scan kernel + mode 0 do in three.
+  // Every CTA first sums b^T c over its share of the chunks of its segment (phase A; operands and
+  // walking direction of problem `pre_prob`; the `gridDim.x` CTAs of a (segment, head) split the
+  // segment's chunks between them) and stores the sum as partial (segment * gridDim.x + blockIdx.x)
+  // of its head in part_out. All CTAs then meet at a grid-wide barrier (the launch must be
+  // cooperative: every CTA resident), after which each CTA adds up the partials of the segments
+  // before its own, takes that as its starting state and runs the attention loop. The last
+  // segment's own sum is never needed and is skipped.
+  int fused;
+  int pre_prob;
+  float* part_out;
+  unsigned bar_slot;   // which pair of g_grid_barriers this launch uses
 };
 
-#ifdef FLA_TRACE
-// Tracing build only: lane 0 of the warps of the first CTA records clock64() at pipeline events,
-// laid out [event][chunk < 64].
-#define FLA_TRACE_DECL                                                                        \
-  const bool trace_on = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 &&          \
-                        blockIdx.z == 0 && (threadIdx.x & 31) == 0;
-#define FLA_TRACE_EVENT(e, i)                                        \
-  do {                                                               \
-    if (trace_on && (i) < 64) p.trace[(e) * 64 + (i)] = clock64();   \
-  } while (0)
-#else
-#define FLA_TRACE_DECL
-#define FLA_TRACE_EVENT(e, i) do { } while (0)
-#endif
+// Barrier words of the fused form: kGridBarSlots pairs (arrival count, generation), zero when the
+// module is loaded and left zero / consistent by every launch (see ptx::grid_barrier). The host
+// hands out the slots round-robin, so launches that may overlap on the GPU use different pairs.
+constexpr int kGridBarSlots = 64;
+static __device__ unsigned g_grid_barriers[2 * kGridBarSlots];
 
 template <int DK, int DV>
 struct Cfg {
@@ -103,7 +122,7 @@ struct Cfg {
   static_assert(NSLOT >= 5, "need at least five tile slots");
   static constexpr int SMEM_BYTES = 1024 + NSLOT * TILE_BYTES + SB_BYTES + OST_BYTES + BAR_BYTES;
   static_assert(SMEM_BYTES <= SMEM_LIMIT, "shared memory budget");
-  static_assert((2 * NSLOT + 10) * 8 + 16 <= BAR_BYTES, "barrier area");
+  static_assert((2 * NSLOT + 12) * 8 + 16 <= BAR_BYTES, "barrier area");
   // TMEM columns (32-bit each, 128 lanes)
   static constexpr int P_COL = 0;         // P fp32: 128 columns
   static constexpr int PB_COL = 128;      // P bf16 (two per column): two buffers of 64 columns
@@ -127,7 +146,6 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
   const int nseg = gridDim.y;
   const int bh = blockIdx.z;
   const int mode = p.mode;
-  FLA_TRACE_DECL
   if (mode == 1 && p.skip_last_segment && g == nseg - 1) return;  // whole CTA, before any setup
 
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -150,8 +168,10 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
   const uint32_t sb_ready = bar_base + 8u * (2 * NSLOT + 3);
   const uint32_t o_free = bar_base + 8u * (2 * NSLOT + 5);
   const uint32_t s_full = bar_base + 8u * (2 * NSLOT + 4);
+  const uint32_t part_done = bar_base + 8u * (2 * NSLOT + 10);  // fused: partial sum stored (256 arrivals)
+  const uint32_t grid_done = bar_base + 8u * (2 * NSLOT + 11);  // fused: the grid barrier was passed
   const uint32_t holder_off =
-      NSLOT * cfg::TILE_BYTES + cfg::SB_BYTES + cfg::OST_BYTES + 8u * (2 * NSLOT + 10);
+      NSLOT * cfg::TILE_BYTES + cfg::SB_BYTES + cfg::OST_BYTES + 8u * (2 * NSLOT + 12);
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem_gen + holder_off);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + holder_off + 4);
 
@@ -164,21 +184,39 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
   const bool tms = (pr.flags & kFlagTotalMinusSuffix) != 0;
   const bool upper_flag = (pr.flags & kFlagUpperMask) != 0;
   const bool exact0 = tms && (pr.flags & kFlagFirstChunkExact) != 0;
-  const bool has_init = (mode == 0) && (pr.s_init != nullptr);
+  // Fused segments: every CTA loads a starting state (possibly all zeros), see phase B below.
+  const bool fused = (mode == 0) && (p.fused != 0);
+  const bool has_init = (mode == 0) && (fused || pr.s_init != nullptr);
+  // Phase A of the fused form: this CTA's share of its segment's chunks, in the scan order of the
+  // problem whose state is being summed. The last segment's sum is not needed by anyone.
+  const Problem& pre = p.prob[fused ? p.pre_prob : prob_idx];
+  const bool pre_desc = (pre.flags & kFlagDescending) != 0;
+  int a_lo = 0, a_iter = 0;
+  if (fused && g < nseg - 1) {
+    const int nsplit = static_cast<int>(gridDim.x);
+    a_lo = n_iter * static_cast<int>(blockIdx.x) / nsplit;
+    a_iter = n_iter * (static_cast<int>(blockIdx.x) + 1) / nsplit - a_lo;
+  }
+  const int t0 = 2 * a_iter;  // the tiles of phase A come first in the ring numbering
   const size_t st_elems = static_cast<size_t>(p.st_rows) * p.st_cols;
-  const size_t st_index = (static_cast<size_t>(bh) * nseg + g) * st_elems;
+  // state arrays are indexed per (head, segment), except in the fused form, whose only such array
+  // is the caller's final state (one per head)
+  const size_t st_index = (p.fused ? static_cast<size_t>(bh)
+                                   : static_cast<size_t>(bh) * nseg + g) * st_elems;
   const bool st_trans = pr.st_trans != 0;
   auto st_off = [&](int row, int col) {
     return st_index + (st_trans ? static_cast<size_t>(col) * p.st_rows + row
                                 : static_cast<size_t>(row) * p.st_cols + col);
   };
-  // Tiles are numbered in load order: chunk i holds tiles tpc*i + {0: q, 1: k, 2: v} (mode 0) or
-  // 2*i + {0: k, 1: v} (mode 1); tile t lives in slot t % NSLOT during ring pass t / NSLOT.
+  // Tiles are numbered in load order: chunk i holds tiles t0 + tpc*i + {0: q, 1: k, 2: v} (mode 0)
+  // or 2*i + {0: k, 1: v} (mode 1, and phase A of the fused form); tile t lives in slot t % NSLOT
+  // during ring pass t / NSLOT.
   const int tpc = (mode == 0) ? 3 : 2;
 
   // ------------------------------------------------------------------ setup
   if (threadIdx.x == 0) {
-    *abort_flag = 0;
+    abort_flag[0] = 0;
+    abort_flag[1] = static_cast<int>(p.wait_limit_kcycles);
     for (int s = 0; s < NSLOT; ++s) {
       ptx::mbar_init(full_bar(s), 1);
       // mode 0: every tile is read by two MMA groups, each followed by a tcgen05.commit arrival
@@ -193,6 +231,8 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
     ptx::mbar_init(sb_ready, 256);
     ptx::mbar_init(o_free, 128);
     ptx::mbar_init(s_full, 1);
+    ptx::mbar_init(part_done, 256);
+    ptx::mbar_init(grid_done, 1);
     ptx::fence_barrier_init();
     ptx::fence_proxy_async_smem();
   }
@@ -208,30 +248,26 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
     ptx::prefetch_tensormap(&pr.k);
     ptx::prefetch_tensormap(&pr.v);
   }
-  FLA_TRACE_EVENT(31, 0);
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  FLA_TRACE_EVENT(31, 1);
 
   // Wait executed by a whole warp; the outcome is made uniform so that the warp never diverges
   // around .sync.aligned instructions.
   auto wait_uniform = [&](uint32_t bar, uint32_t parity) {
-#ifdef FLA_WAIT_LANE0
-    int ok = 1;
-    if (lane == 0) ok = ptx::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
-    return __shfl_sync(0xffffffffu, ok, 0) != 0;
-#else
     const int ok = ptx::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
     return __all_sync(0xffffffffu, ok) != 0;
-#endif
   };
   auto mem_chunk = [&](int i) {
     return descending ? (p.nchunks - 1 - (chunk0 + i)) : (chunk0 + i);
   };
   // chunk i is computed without the state (see kFlagFirstChunkExact)
   auto plain_chunk = [&](int i) { return exact0 && mem_chunk(i) == 0; };
+  auto pre_mem_chunk = [&](int i) {
+    const int c = chunk0 + a_lo + i;
+    return pre_desc ? (p.nchunks - 1 - c) : c;
+  };
   auto slot_addr = [&](int t) {
     return smem_base + static_cast<uint32_t>(t % NSLOT) * cfg::TILE_BYTES;
   };
@@ -241,28 +277,33 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
     // The whole warp runs the loop (so that addresses and coordinates stay warp-uniform); one
     // elected lane issues. In mode 0 the q and k tiles of a chunk complete on the q tile's barrier.
     const bool leader = ptx::elect_one();
-    const int n_tiles = n_iter * tpc;
+    const int n_tiles = t0 + n_iter * tpc;
     for (int t = 0; t < n_tiles; ++t) {
       const int s = t % NSLOT;
       const uint32_t ph = (t / NSLOT) & 1;
       if (!wait_uniform(empty_bar(s), ph ^ 1u)) break;
-      const int i = t / tpc;
-      const int which = t - i * tpc + (mode == 0 ? 0 : 1);  // 0 q, 1 k, 2 v
-      const CUtensorMap* map = (which == 0) ? &pr.q : (which == 1 ? &pr.k : &pr.v);
+      const bool phase_a = t < t0;  // k, v tiles of the summed problem, each on its own barrier
+      const int tt = phase_a ? t : t - t0;
+      const int i = phase_a ? (tt >> 1) : tt / tpc;
+      const int which = phase_a ? 1 + (tt & 1) : tt - i * tpc + (mode == 0 ? 0 : 1);  // 0 q, 1 k, 2 v
+      const Problem& src = phase_a ? pre : pr;
+      const CUtensorMap* map = (which == 0) ? &src.q : (which == 1 ? &src.k : &src.v);
       const uint32_t dst = slot_addr(t);
-      const int tok = mem_chunk(i) * kChunk;
+      const int tok = (phase_a ? pre_mem_chunk(i) : mem_chunk(i)) * kChunk;
+      const bool paired = mode == 0 && !phase_a;  // q and k of a chunk complete on q's barrier
       // barrier that the tile's bytes complete on, and the bytes armed on it at this point
-      const uint32_t bar = (mode == 0 && which == 1) ? full_bar((t - 1) % NSLOT) : full_bar(s);
+      const uint32_t bar = (paired && which == 1) ? full_bar((t - 1) % NSLOT) : full_bar(s);
       if (leader) {
-        if (mode == 0 && which == 0) ptx::mbar_expect_tx(bar, 2 * cfg::TILE_BYTES);
-        if (mode != 0 || which == 2) ptx::mbar_expect_tx(bar, cfg::TILE_BYTES);
+        if (paired && which == 0) ptx::mbar_expect_tx(bar, 2 * cfg::TILE_BYTES);
+        if (!paired || which == 2) ptx::mbar_expect_tx(bar, cfg::TILE_BYTES);
         // The k slot's own barrier is not waited on; complete its phase so that the parity of
         // later ring passes stays in step.
-        if (mode == 0 && which == 1) ptx::mbar_arrive(full_bar(s));
+        if (paired && which == 1) ptx::mbar_arrive(full_bar(s));
+        if (!(p.debug_withhold && t == 0)) {
 #pragma unroll
-        for (int gg = 0; gg < cfg::GK; ++gg)
-          ptx::tma_load_4d(dst + gg * kGroupBytes, map, bar, gg * 64, tok, h, b);
-        FLA_TRACE_EVENT(28 + which, i);
+          for (int gg = 0; gg < cfg::GK; ++gg)
+            ptx::tma_load_4d(dst + gg * kGroupBytes, map, bar, gg * 64, tok, h, b);
+        }
       }
       __syncwarp();
     }
@@ -288,9 +329,9 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
     };
     // P = Q K^T of chunk i (both operands K-major, 16 columns of dk per instruction)
     auto issue_qk = [&](int i) {
-      if (!wait_tile(3 * i)) return false;  // covers the k tile too
-      const uint32_t q_lo = ptx::desc_lo(slot_addr(3 * i), 16);
-      const uint32_t k_lo = ptx::desc_lo(slot_addr(3 * i + 1), 16);
+      if (!wait_tile(t0 + 3 * i)) return false;  // covers the k tile too
+      const uint32_t q_lo = ptx::desc_lo(slot_addr(t0 + 3 * i), 16);
+      const uint32_t k_lo = ptx::desc_lo(slot_addr(t0 + 3 * i + 1), 16);
       if (leader) {
 #pragma unroll
         for (int kk = 0; kk < DK / 16; ++kk) {
@@ -299,20 +340,42 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         }
         ptx::tc_commit(p_full);
       }
-      release_tile(3 * i);      // first of two arrivals on q (the other: issuer Y after Q Sb)
-      release_tile(3 * i + 1);  // first of two arrivals on k (the other: below, after K^T V)
+      release_tile(t0 + 3 * i);      // first of two arrivals on q (the other: issuer Y after Q Sb)
+      release_tile(t0 + 3 * i + 1);  // first of two arrivals on k (the other: below, after K^T V)
       __syncwarp();
       return true;
     };
     if (mode == 0) {
       uint32_t sb_waits = 0;
-      bool ok = issue_qk(0);
+      bool ok = true;
+      // ---- phase A of the fused form: plain sum of b^T c over this CTA's share of the segment
+      // (always added, whatever sign the CTA's own product uses), read out by the converters
+      for (int i = 0; ok && i < a_iter; ++i) {
+        if (!wait_tile(2 * i) || !wait_tile(2 * i + 1)) { ok = false; break; }
+        const uint32_t k_lo = ptx::desc_lo(slot_addr(2 * i), kGroupBytes);
+        const uint32_t v_lo = ptx::desc_lo(slot_addr(2 * i + 1), kGroupBytes);
+        ptx::tc_fence_after();
+        if (leader) {
+#pragma unroll
+          for (int kk = 0; kk < kChunk / 16; ++kk) {
+            ptx::mma_ss(tS, k_lo + kk * (2048 >> 4), v_lo + kk * (2048 >> 4), ptx::kDescHi,
+                        IDESC_KV_ADD, (i > 0 || kk > 0) ? 1u : 0u);
+          }
+          // the ring's barriers expect two consumers per tile in mode 0
+          ptx::tc_commit(empty_bar((2 * i) % NSLOT));
+          ptx::tc_commit(empty_bar((2 * i) % NSLOT));
+          ptx::tc_commit(empty_bar((2 * i + 1) % NSLOT));
+          ptx::tc_commit(empty_bar((2 * i + 1) % NSLOT));
+          if (i == a_iter - 1) ptx::tc_commit(s_full);
+        }
+        __syncwarp();
+      }
+      ok = ok && issue_qk(0);
       for (int i = 0; ok && i < n_iter; ++i) {
         // k, v MN-major: 64-column groups kGroupBytes apart
-        const uint32_t k_lo = ptx::desc_lo(slot_addr(3 * i + 1), kGroupBytes);
-        const uint32_t v_lo = ptx::desc_lo(slot_addr(3 * i + 2), kGroupBytes);
+        const uint32_t k_lo = ptx::desc_lo(slot_addr(t0 + 3 * i + 1), kGroupBytes);
+        const uint32_t v_lo = ptx::desc_lo(slot_addr(t0 + 3 * i + 2), kGroupBytes);
         const bool have_state = (i > 0) || has_init;
-        FLA_TRACE_EVENT(0, i);
         // ---- S += K^T V  (both operands MN-major: the token index is the MMA K dimension).
         // For DK = 64 the instruction still spans 128 rows; the upper 64 read whatever follows
         // the K tile in shared memory and land in TMEM lanes nobody reads.
@@ -320,9 +383,7 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
           if (!wait_uniform(sb_ready, sb_waits & 1)) break;
           ++sb_waits;
         }
-        FLA_TRACE_EVENT(2, i);
-        if (!wait_tile(3 * i + 2)) break;
-        FLA_TRACE_EVENT(4, i);
+        if (!wait_tile(t0 + 3 * i + 2)) break;
         ptx::tc_fence_after();
         if (leader) {
 #pragma unroll
@@ -332,24 +393,19 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
           }
           ptx::tc_commit(s_full);
         }
-        release_tile(3 * i + 1);
-        release_tile(3 * i + 2);  // first of two arrivals on v (the other: issuer Y after P V)
-        FLA_TRACE_EVENT(5, i);
+        release_tile(t0 + 3 * i + 1);
+        release_tile(t0 + 3 * i + 2);  // first of two arrivals on v (the other: issuer Y after P V)
         // ---- score tile of the next chunk
         if (i + 1 < n_iter) {
           if (!wait_uniform(p_read, i & 1)) break;
           if (i >= 1 && !wait_uniform(((i - 1) & 1) ? o_full1 : o_full0, ((i - 1) >> 1) & 1)) break;
-          FLA_TRACE_EVENT(6, i);
           ptx::tc_fence_after();
           ok = issue_qk(i + 1);
         }
-        FLA_TRACE_EVENT(8, i);
       }
     } else {
       for (int i = 0; i < n_iter; ++i) {
-        FLA_TRACE_EVENT(0, i);
         if (!wait_tile(2 * i) || !wait_tile(2 * i + 1)) break;
-        FLA_TRACE_EVENT(4, i);
         const uint32_t k_lo = ptx::desc_lo(slot_addr(2 * i), kGroupBytes);
         const uint32_t v_lo = ptx::desc_lo(slot_addr(2 * i + 1), kGroupBytes);
         if (leader) {
@@ -381,19 +437,17 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       auto wait_tile = [&](int t) { return wait_uniform(full_bar(t % NSLOT), (t / NSLOT) & 1); };
       uint32_t sb_waits = 0;
       for (int i = 0; i < n_iter; ++i) {
-        const uint32_t q_lo = ptx::desc_lo(slot_addr(3 * i), 16);                // K-major
-        const uint32_t v_lo = ptx::desc_lo(slot_addr(3 * i + 2), kGroupBytes);  // MN-major
+        const uint32_t q_lo = ptx::desc_lo(slot_addr(t0 + 3 * i), 16);                // K-major
+        const uint32_t v_lo = ptx::desc_lo(slot_addr(t0 + 3 * i + 2), kGroupBytes);  // MN-major
         const bool have_state = (i > 0) || has_init;
         const bool use_state = have_state && !plain_chunk(i);
         const uint32_t tPb = tmem_base + cfg::PB_COL + (i & 1) * 64;
-        FLA_TRACE_EVENT(9, i);
         if (i >= 1 && !wait_uniform(o_free, (i - 1) & 1)) break;
         if (have_state) {
           if (!wait_uniform(sb_ready, sb_waits & 1)) break;
           ++sb_waits;
         }
-        if (!wait_tile(3 * i)) break;
-        FLA_TRACE_EVENT(17, i);
+        if (!wait_tile(t0 + 3 * i)) break;
         ptx::tc_fence_after();
         if (leader) {
           if (use_state) {
@@ -405,12 +459,10 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
             }
           }
           ptx::tc_commit(qs_done);
-          ptx::tc_commit(empty_bar((3 * i) % NSLOT));  // second arrival on q
+          ptx::tc_commit(empty_bar((t0 + 3 * i) % NSLOT));  // second arrival on q
         }
-        FLA_TRACE_EVENT(18, i);
         if (!wait_uniform(pb_ready, i & 1)) break;
-        if (!wait_tile(3 * i + 2)) break;
-        FLA_TRACE_EVENT(19, i);
+        if (!wait_tile(t0 + 3 * i + 2)) break;
         ptx::tc_fence_after();
         if (leader) {
 #pragma unroll
@@ -419,10 +471,9 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
                         kk > 0 ? 1u : (use_state ? 1u : 0u));
           }
           ptx::tc_commit((i & 1) ? o_full1 : o_full0);
-          ptx::tc_commit(empty_bar((3 * i + 2) % NSLOT));  // second arrival on v
+          ptx::tc_commit(empty_bar((t0 + 3 * i + 2) % NSLOT));  // second arrival on v
         }
         __syncwarp();
-        FLA_TRACE_EVENT(7, i);
       }
     }
   } else if (warp < 10) {
@@ -498,47 +549,150 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       }
     };
 
-    if (has_init) {
-      const float* src = pr.s_init;
+    bool conv_ok = true;
+    if (fused) {
+      // ---------------- phase A read-out: this CTA's partial sum -> part_out (scratch layout,
+      // one thread per state row), then the grid-wide barrier. Every CTA of the grid takes part
+      // in the barrier, whether it had chunks to sum or not.
+      if (a_iter > 0) {
+        int ok = ptx::mbar_wait(s_full, 0, abort_flag) ? 1 : 0;
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+          ptx::tc_fence_after();
+          const size_t slot = static_cast<size_t>(bh) * (static_cast<size_t>(nseg) * gridDim.x) +
+                              static_cast<size_t>(g) * gridDim.x + blockIdx.x;
+          float* dst = p.part_out + slot * st_elems;
+#pragma unroll 1
+          for (int jb = 0; jb < SBLK; ++jb) {
+            const int cb = half * SBLK + jb;
+            ptx::tmem_ld32(lane_base + cfg::S_COL + cb * 32, ra);
+            ptx::tc_wait_ld();
+            if (row < p.st_rows) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (cb * 32 + j < p.st_cols)
+                  __stcg(dst + static_cast<size_t>(cb * 32 + j) * p.st_rows + row, __uint_as_float(ra[j]));
+            }
+          }
+          ptx::tc_fence_before();
+        }
+        conv_ok = ok != 0;
+      }
+      __threadfence();  // the partial sum is visible device-wide before this thread reports it stored
+      if (conv_ok) ptx::mbar_arrive(part_done);
+      if (warp == 2) {
+        // One warp per CTA arrives at the grid barrier once all 256 converter threads have stored
+        // (and fenced) their share, waits for the other CTAs, and releases the rest of the group.
+        bool ok = wait_uniform(part_done, 0);
+        if (ok) {
+          int passed = 1;
+          if (lane == 0) passed = ptx::grid_barrier(&g_grid_barriers[2 * (p.bar_slot % kGridBarSlots)],
+                                             gridDim.x * gridDim.y * gridDim.z, abort_flag) ? 1 : 0;
+          ok = __shfl_sync(0xffffffffu, passed, 0) != 0;
+        }
+        if (ok && lane == 0) ptx::mbar_arrive(grid_done);
+      }
+      if (conv_ok) {
+        int ok = ptx::mbar_wait(grid_done, 0, abort_flag) ? 1 : 0;
+        conv_ok = __all_sync(0xffffffffu, ok) != 0;
+      }
+    }
+
+    if (has_init && conv_ok) {
+      // One 32-column block of a [st_rows][st_cols] state array (transposed storage if `trans`)
+      // into this thread's row registers; zero outside the valid part. Loads bypass L1: in the
+      // fused form the arrays were written by other CTAs of this launch.
+      auto load_block = [&](int cb, const float* ptr, size_t index0, bool trans, uint32_t (&out)[32]) {
+        if (kStagedStateIO && !trans) {
+          const uint32_t base = ost_addr;  // the output staging buffer is idle before chunk 0
+          const int col = cb * 32 + lane;
+#pragma unroll 4
+          for (int rr = 0; rr < 32; ++rr) {
+            const int grow = quad * 32 + rr;
+            float x = 0.f;
+            if (grow < p.st_rows && col < p.st_cols)
+              x = __ldcg(ptr + index0 + static_cast<size_t>(grow) * p.st_cols + col);
+            ptx::st_shared_b32(xpose_addr(base, lane, rr), __float_as_uint(x));
+          }
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) out[j] = ptx::ld_shared_b32(xpose_addr(base, j, lane));
+          __syncwarp();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = cb * 32 + j;
+            float x = 0.f;
+            if (row < p.st_rows && col < p.st_cols)
+              x = __ldcg(ptr + index0 + (trans ? static_cast<size_t>(col) * p.st_rows + row
+                                               : static_cast<size_t>(row) * p.st_cols + col));
+            out[j] = __float_as_uint(x);
+          }
+        }
+      };
+      auto accumulate = [&](const uint32_t (&x)[32]) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          ra[j] = __float_as_uint(__uint_as_float(ra[j]) + __uint_as_float(x[j]));
+      };
+      const size_t head_index = static_cast<size_t>(bh) * st_elems;
 #pragma unroll 1
       for (int jb = 0; jb < SBLK; ++jb) {
         const int cb = half * SBLK + jb;
-        // One 32-column block of a [st_rows][st_cols] state array (transposed storage if `trans`)
-        // into this thread's row registers; zero outside the valid part.
-        auto load_block = [&](const float* ptr, size_t index0, bool trans, uint32_t (&out)[32]) {
-          if (kStagedStateIO && !trans) {
-            const uint32_t base = ost_addr;  // the output staging buffer is idle before chunk 0
-            const int col = cb * 32 + lane;
-#pragma unroll 4
-            for (int rr = 0; rr < 32; ++rr) {
-              const int grow = quad * 32 + rr;
-              float x = 0.f;
-              if (grow < p.st_rows && col < p.st_cols)
-                x = ptr[index0 + static_cast<size_t>(grow) * p.st_cols + col];
-              ptx::st_shared_b32(xpose_addr(base, lane, rr), __float_as_uint(x));
-            }
-            __syncwarp();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) out[j] = ptx::ld_shared_b32(xpose_addr(base, j, lane));
-            __syncwarp();
+        if (!fused) {
+          load_block(cb, pr.s_init, st_index, st_trans, ra);
+          if (pr.s_add != nullptr) {
+            load_block(cb, pr.s_add, head_index, pr.add_trans != 0, rb);
+            accumulate(rb);
+          }
+        } else {
+          // caller's state (every segment for kInitParts, the first one only for kInitBound)
+          const bool bound = pr.init_kind == kInitBound;
+          if (pr.s_add != nullptr && (!bound || g == 0)) {
+            load_block(cb, pr.s_add, head_index, pr.add_trans != 0, ra);
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int col = cb * 32 + j;
-              float x = 0.f;
-              if (row < p.st_rows && col < p.st_cols)
-                x = ptr[index0 + (trans ? static_cast<size_t>(col) * p.st_rows + row
-                                        : static_cast<size_t>(row) * p.st_cols + col)];
-              out[j] = __float_as_uint(x);
+            for (int j = 0; j < 32; ++j) ra[j] = 0u;
+          }
+          const bool itrans = pr.init_trans != 0;
+          if (bound) {
+            if (g > 0) {
+              const size_t slot = static_cast<size_t>(bh) * pr.init_stride + (pr.bound_slot0 - g * pr.bound_step);
+              load_block(cb, pr.init_base, slot * st_elems, itrans, rb);
+              accumulate(rb);
+            }
+          } else {
+            // partial sums of all earlier segments, two in flight at a time
+            const int nsplit = static_cast<int>(gridDim.x);
+            const size_t slot0 = static_cast<size_t>(bh) * (static_cast<size_t>(nseg) * nsplit);
+            const int nsrc = g * nsplit;
+            // a CTA whose share of its segment was empty (fewer chunks than CTAs) stored nothing
+            auto next_stored = [&](int j) {
+              while (j < nsrc) {
+                const int x = j % nsplit;
+                if (p.seg_chunks * (x + 1) / nsplit - p.seg_chunks * x / nsplit > 0) break;
+                ++j;
+              }
+              return j;
+            };
+            uint32_t rc[32];
+            int j = next_stored(0);
+            while (j < nsrc) {
+              const int j2 = next_stored(j + 1);
+              load_block(cb, pr.init_base, (slot0 + j) * st_elems, itrans, rb);
+              if (j2 < nsrc) load_block(cb, pr.init_base, (slot0 + j2) * st_elems, itrans, rc);
+              accumulate(rb);
+              if (j2 < nsrc) accumulate(rc);
+              j = j2 < nsrc ? next_stored(j2 + 1) : nsrc;
             }
           }
-        };
-        load_block(src, st_index, st_trans, ra);
-        if (pr.s_add != nullptr) {
-          load_block(pr.s_add, static_cast<size_t>(bh) * st_elems, pr.add_trans != 0, rb);
+          if (pr.bound_out != nullptr && g > 0 && row < p.st_rows) {
+            float* dst = pr.bound_out + (static_cast<size_t>(bh) * (nseg - 1) + (g - 1)) * st_elems;
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            ra[j] = __float_as_uint(__uint_as_float(ra[j]) + __uint_as_float(rb[j]));
+            for (int j = 0; j < 32; ++j)
+              if (cb * 32 + j < p.st_cols)
+                __stcg(dst + static_cast<size_t>(cb * 32 + j) * p.st_rows + row, __uint_as_float(ra[j]));
+          }
         }
         ptx::tmem_st32(lane_base + cfg::S_COL + cb * 32, ra);
         if (row < DK) store_sb(cb, ra);
@@ -547,17 +701,16 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before();
       ptx::mbar_arrive(sb_ready);
-      if (warp == 2) FLA_TRACE_EVENT(31, 2);
     }
 
+    // phase A, if it ran, used the first phase of s_full
+    const uint32_t s_off = a_iter > 0 ? 1u : 0u;
     if (mode == 0) {
-      for (int i = 0; i < n_iter; ++i) {
+      for (int i = 0; conv_ok && i < n_iter; ++i) {
         // ---------------- P: fp32 -> causal mask -> bf16 A operand (this group's 64 columns)
-        if (warp == 2) FLA_TRACE_EVENT(10, i);
         int ok = ptx::mbar_wait(p_full, i & 1, abort_flag) ? 1 : 0;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (warp == 2) FLA_TRACE_EVENT(11, i);
         ptx::tc_fence_after();
         // Column blocks of 32: relative to this warp's 32 rows a block is entirely kept, entirely
         // masked, or (block index == quadrant) the diagonal block that needs per-element tests.
@@ -616,44 +769,37 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         } else {
           p_convert(std::integral_constant<int, 0>{});
         }
-        if (warp == 2) FLA_TRACE_EVENT(12, i);
         ptx::tc_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive(pb_ready);
-        if (warp == 2) FLA_TRACE_EVENT(13, i);
 
         // ---------------- S: fp32 -> bf16 B operand for the next chunk (or -> s_final)
         const bool last = (i == n_iter - 1);
         const bool to_final = last && (pr.s_final != nullptr) && (g == nseg - 1);
         if (!last || to_final) {
-          ok = ptx::mbar_wait(s_full, i & 1, abort_flag) ? 1 : 0;
+          ok = ptx::mbar_wait(s_full, (i + s_off) & 1, abort_flag) ? 1 : 0;
           // the state buffer is still the B operand of issuer Y's Q Sb of this chunk
           // (also before a final-state write, which borrows that buffer as transpose scratch)
           if (ok) ok = ptx::mbar_wait(qs_done, i & 1, abort_flag) ? 1 : 0;
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
-          if (warp == 2) FLA_TRACE_EVENT(14, i);
           ptx::tc_fence_after();
           convert_state(!last, to_final);
-          if (warp == 2) FLA_TRACE_EVENT(15, i);
           if (!last) {
             ptx::fence_proxy_async_smem();
             ptx::tc_fence_before();
             ptx::mbar_arrive(sb_ready);
           }
-          if (warp == 2) FLA_TRACE_EVENT(16, i);
         }
       }
     } else {
       // state only: one read-out after the last chunk
       int ok = ptx::mbar_wait(s_full, 0, abort_flag) ? 1 : 0;
       ok = __all_sync(0xffffffffu, ok);
-      if (warp == 2) FLA_TRACE_EVENT(31, 3);
       if (ok && pr.s_final != nullptr) {
         ptx::tc_fence_after();
         convert_state(false, true);
       }
-      if (warp == 2) FLA_TRACE_EVENT(31, 4);
     }
   } else {
     // ================================================================ epilogue group
@@ -665,11 +811,9 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       uint32_t ra[32], rb[32];
       uint32_t pk[DV / 2];
       for (int i = 0; i < n_iter; ++i) {
-        if (warp == 10) FLA_TRACE_EVENT(20, i);
         int ok = ptx::mbar_wait((i & 1) ? o_full1 : o_full0, (i >> 1) & 1, abort_flag) ? 1 : 0;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (warp == 10) FLA_TRACE_EVENT(21, i);
         ptx::tc_fence_after();
 #pragma unroll
         for (int cb = 0; cb < DV / 32; cb += 2) {
@@ -686,7 +830,6 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         }
         ptx::tc_fence_before();
         ptx::mbar_arrive(o_free);
-        if (warp == 10) FLA_TRACE_EVENT(22, i);
         // Every warp stages and stores its own 32 rows (a 64 x 32 box per column group), so no
         // barrier spans the group and nobody waits for a store except the warp that issued it:
         // before overwriting its rows, lane 0 checks that the previous store has read them.
@@ -704,7 +847,6 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         }
         ptx::fence_proxy_async_smem();
         __syncwarp();
-        if (warp == 10) FLA_TRACE_EVENT(23, i);
         const int tok = mem_chunk(i) * kChunk + quad * 32;
         if (lane == 0 && tok < pr.n_tokens) {
 #pragma unroll
@@ -712,7 +854,6 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
             ptx::tma_store_4d(&pr.o, ost_addr + gg * kGroupBytes + quad * (32 * 128), gg * 64, tok,
                               h, b);
           ptx::bulk_commit_group();
-          FLA_TRACE_EVENT(24, i);
         }
       }
       if (lane == 0) ptx::bulk_wait_group0();
@@ -722,7 +863,6 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
 
   // ------------------------------------------------------------------ teardown
   __syncwarp();
-  FLA_TRACE_EVENT(31, 5 + (warp < 15 ? warp : 0));
   if (*abort_flag) {
     // A wait gave up: let copies in flight land before the shared memory is released.
     __nanosleep(100000);

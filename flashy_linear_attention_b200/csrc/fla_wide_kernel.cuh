@@ -38,6 +38,8 @@ struct WideParams {
   int nchunks;
   int da;            // valid columns of a and b
   int* status;       // device word, bit 0 set when a bounded wait ran out; may be null
+  unsigned wait_limit_kcycles;  // limit of one bounded wait in units of 1024 SM cycles; 0 = default
+  int debug_withhold;  // test hook: the first c tile is never loaded, so the waits on it run out
 };
 
 constexpr int kWideThreads = 448;
@@ -106,7 +108,8 @@ fla_wide_kernel(const __grid_constant__ WideParams p) {
   auto pair_cols = [&](int t) { return max(0, min(128, p.da - 128 * t)); };
 
   if (threadIdx.x == 0) {
-    *abort_flag = 0;
+    abort_flag[0] = 0;
+    abort_flag[1] = static_cast<int>(p.wait_limit_kcycles);
     for (int s = 0; s < kWideSlots; ++s) {
       ptx::mbar_init(full_bar(s), 1);
       ptx::mbar_init(empty_bar(s), 1);
@@ -171,7 +174,8 @@ fla_wide_kernel(const __grid_constant__ WideParams p) {
       if (!wait_uniform(cempty_bar(cs), ((i >> 1) & 1) ^ 1u)) break;
       if (leader) {
         ptx::mbar_expect_tx(cfull_bar(cs), kWideGroupBytes);
-        ptx::tma_load_4d(c_addr + cs * kWideGroupBytes, &p.c, cfull_bar(cs), 0, tok, h, b);
+        if (!(p.debug_withhold && i == 0))
+          ptx::tma_load_4d(c_addr + cs * kWideGroupBytes, &p.c, cfull_bar(cs), 0, tok, h, b);
       }
       for (int t = 0; t < NT; ++t) {
         const int groups = pair_groups(t);  // a group that is all padding is not loaded

@@ -54,28 +54,66 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return done;
 }
 
-// Limit of one wait in SM clock cycles (about 0.4 s at 2 GHz): far above any legitimate wait of
-// these kernels, which are microseconds.
+// Default limit of one wait in SM clock cycles (about 0.4 s at 2 GHz): far above any legitimate
+// wait of these kernels, which are microseconds.
 constexpr long long kWaitLimitCycles = 800ll * 1000ll * 1000ll;
 
 // Waits for the phase with the given parity. Returns false when the CTA-wide abort flag is set
 // or the limit ran out (in which case it sets the flag so that every other wait of the CTA
-// gives up too).
+// gives up too). `abort_flag` points at two shared-memory words: [0] the flag, [1] the limit in
+// units of 1024 cycles (0 = kWaitLimitCycles), which the host can shorten for tests.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
 #pragma unroll 1
   for (int spin = 0; spin < 64; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
   }
   const long long t0 = clock64();
+  const unsigned lim_k = static_cast<unsigned>(abort_flag[1]);
+  const long long limit = lim_k ? (static_cast<long long>(lim_k) << 10) : kWaitLimitCycles;
 #pragma unroll 1
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit) {
         *abort_flag = 1;
         return false;
       }
+    }
+  }
+}
+
+// Grid-wide barrier for a launch whose CTAs are all resident (cooperative launch). Called by ONE
+// thread per CTA, after the CTA's earlier global writes have been fenced. bar[0] counts arrivals,
+// bar[1] is the generation; the last arrival resets the count and bumps the generation, so the two
+// words need no initialisation beyond being zero before their first use. The wait is bounded like
+// every other wait here; a CTA that gives up withdraws its arrival and sets the abort flag.
+__device__ __forceinline__ bool grid_barrier(unsigned* bar, unsigned n_ctas, volatile int* abort_flag) {
+  unsigned gen;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(gen) : "l"(bar + 1) : "memory");
+  __threadfence();
+  const unsigned prev = atomicAdd(bar, 1u);
+  if (prev == n_ctas - 1u) {
+    bar[0] = 0u;
+    __threadfence();
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(bar + 1), "r"(gen + 1u) : "memory");
+    return true;
+  }
+  const long long t_start = clock64();
+  const unsigned lim_k = static_cast<unsigned>(abort_flag[1]);
+  const long long limit = lim_k ? (static_cast<long long>(lim_k) << 10) : kWaitLimitCycles;
+#pragma unroll 1
+  for (uint32_t spin = 1;; ++spin) {
+    unsigned now;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(now) : "l"(bar + 1) : "memory");
+    if (now != gen) {
+      __threadfence();
+      return true;
+    }
+    if ((spin & 15u) == 0u && (*abort_flag || clock64() - t_start > limit)) {
+      atomicSub(bar, 1u);
+      *abort_flag = 1;
+      return false;
     }
   }
 }

@@ -44,8 +44,14 @@ def _forward_with_state(ctx: Any, q, k, v, smallv: bool):
     ops.check_forward_preconditions(q, v, smallv)
     B, H, _, dk = q.shape
     s_final = torch.empty(B * H, dk, v.shape[-1], dtype=torch.float32, device=q.device)
-    out = ops.causal_dot_product_fwd(q, k, v, s_final=s_final)
-    ctx.save_for_backward(q, k, v, s_final)
+    # few heads per GPU: the forward is split into segments and also hands the state at the segment
+    # boundaries to the backward
+    seg_states = ops.segment_states_buffer(q, v)
+    out = ops.causal_dot_product_fwd(q, k, v, s_final=s_final, seg_states=seg_states)
+    if seg_states is None:
+        ctx.save_for_backward(q, k, v, s_final)
+    else:
+        ctx.save_for_backward(q, k, v, s_final, seg_states)
     ctx.has_state = True
     return out
 
@@ -57,8 +63,9 @@ def _backward_with_state(ctx: Any, grad_output, smallv: bool):
             return ops.causal_dot_product_bwd(grad_output, query, key, value, keep_padded=True)
         fn = linear_flash_wrapper_bwd_smallv_hd if smallv else linear_flash_wrapper_bwd
         return fn(grad_output, query, key, value)
-    query, key, value, s_final = ctx.saved_tensors
-    return ops.causal_dot_product_bwd(grad_output, query, key, value, s_last=s_final)
+    query, key, value, s_final = ctx.saved_tensors[:4]
+    seg_states = ctx.saved_tensors[4] if len(ctx.saved_tensors) > 4 else None
+    return ops.causal_dot_product_bwd(grad_output, query, key, value, s_last=s_final, seg_states=seg_states)
 
 
 class LinearAttention(Function):
@@ -98,7 +105,10 @@ class LinearAttentionResumable(Function):
     ``s_final`` are fp32 ``[batch, heads, dk, dv]`` (sum of k_j^T v_j over the tokens before /
     up to the end of this call; ``s_init=None`` starts from zero). Feeding ``s_final`` of one call
     as ``s_init`` of the next gives what one call over the concatenated tokens gives: chunked
-    prefill, recurrent decoding, or training on a long sequence piece by piece. The state is
+    prefill, decoding a few tokens at a time, or training on a long sequence piece by piece. Any
+    number of tokens per call is accepted (the reference's multiple-of-64 rule,
+    linear_attn_kernels.py:323-325, is a property of its tiling; a call of one token still costs a
+    whole 128-token tile here, so decode in blocks where possible). The state is
     differentiable: the backward returns the gradient of ``s_init`` and accepts one for ``s_final``.
 
     Not part of the reference, whose Functions (flashlinear/linear_attn.py:11-31) always start from
@@ -108,7 +118,8 @@ class LinearAttentionResumable(Function):
     @staticmethod
     @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
     def forward(ctx: Any, q, k, v, s_init=None):
-        ops.check_forward_preconditions(q, v, smallv=q.shape[-1] != v.shape[-1])
+        assert q.shape[-1] <= ops.KERNEL_HEAD_DIM and v.shape[-1] <= ops.KERNEL_HEAD_DIM, \
+            f"Only head_dims <= {ops.KERNEL_HEAD_DIM} are supported."
         B, H, _, dk = q.shape
         dv = v.shape[-1]
         if s_init is not None:

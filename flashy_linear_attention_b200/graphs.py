@@ -8,8 +8,9 @@ ctypes round trips, which matters when a GPU holds few heads (a step of 0.07-0.1
     step = capture_step(lambda: ops.causal_dot_product_bwd(dy, q, k, v))
     grads = step()        # replays; returns the tensors the captured call returned
 
-Not for calls whose arguments must change between launches (the peer state exchange carries an
-epoch counter).
+Calls whose arguments change between launches cannot be replayed. The peer state exchange is not
+one of them when its exchange count lives on the device (`PeerStateExchange` does that), so a
+sequence-sharded step can be captured as well.
 """
 from __future__ import annotations
 

@@ -103,11 +103,12 @@ class HostPipeline:
                 arrived.record(self._h2d)
             cur.wait_event(arrived)
             qs, ks, vs, gs = (t[:n].unsqueeze(0) for t in stage)
-            state = None
+            state = seg_states = None
             if ops.backward_uses_final_state(qs, vs):
                 state = torch.empty(n, qs.shape[-1], vs.shape[-1], dtype=torch.float32, device=self.device)
-            o = ops.causal_dot_product_fwd(qs, ks, vs, s_final=state)
-            grads = ops.causal_dot_product_bwd(gs, qs, ks, vs, s_last=state)
+                seg_states = ops.segment_states_buffer(qs, vs)
+            o = ops.causal_dot_product_fwd(qs, ks, vs, s_final=state, seg_states=seg_states)
+            grads = ops.causal_dot_product_bwd(gs, qs, ks, vs, s_last=state, seg_states=seg_states)
             done = torch.cuda.Event()
             done.record(cur)
             computed[slot] = done

@@ -24,6 +24,16 @@ MAX_HEAD_DIM = 256     # cap of LinearAttention, as in the reference (linear_att
 MAX_HEAD_DIM_QK_SMALLV = 512  # cap of q/k for LinearAttentionSmallVHD (273-dim Taylor features fit)
 
 _status_words = {}
+# FLA_DEBUG_* bits passed with every call; FLA_DEBUG_FLAGS in the environment sets the initial value
+_debug_flags = int(os.environ.get("FLA_DEBUG_FLAGS", "0") or 0)
+
+
+def set_debug_flags(flags: int) -> int:
+    """Sets the FLA_DEBUG_* bits passed with every later call (0 in production) and returns the
+    previous value. Used by tests, e.g. to keep the three-launch segmented form for comparison."""
+    global _debug_flags
+    old, _debug_flags = _debug_flags, int(flags)
+    return old
 
 
 def _next_pow2(x: int) -> int:
@@ -169,6 +179,7 @@ def _call(pass_id: int, args: FlaArgs, device: torch.device, which: int = 0,
     with torch.cuda.device(device):
         args.stream = torch.cuda.current_stream(device).cuda_stream
         args.status = _status_word(device).data_ptr()
+        args.debug_flags = _debug_flags
         need = lib.fla_sm100_workspace_bytes(ctypes.byref(args), 0 if pass_id == 3 else pass_id)
         ws = workspace
         if ws is not None:
@@ -214,7 +225,9 @@ def _native_dims(da: int, dc: int) -> bool:
 def _product_sliced(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, like: torch.Tensor, anticausal: bool) -> torch.Tensor:
     """Causal product for head dims above the kernels' 128-wide tiles, by linearity: output columns
     are independent (slices of c), and (a_i . b_j) is the sum over slices of the a/b head dim, so
-    the partial products of those slices are added (fp32) before the one rounding to bf16."""
+    the partial products of those slices are added. Each partial product leaves its kernel rounded
+    to bf16; the sum of the (at most two) partials is formed in fp32 and rounded once more, so a
+    result with both head dims above 128 carries up to three bf16 roundings instead of one."""
     av, bv, cv = _kernel_view(a), _kernel_view(b), _kernel_view(c)
     da, dc = a.shape[-1], c.shape[-1]
     W = KERNEL_HEAD_DIM
@@ -247,6 +260,7 @@ def causal_dot_product_fwd(
     s_final: Optional[torch.Tensor] = None,
     segments: int = 0,
     segment_workspace: Optional[torch.Tensor] = None,
+    seg_states: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """out[b,h,i] = sum_{j<=i} (q_i . k_j) v_j, bf16 in / bf16 out, fp32 accumulation.
 
@@ -255,6 +269,9 @@ def causal_dot_product_fwd(
     segment_workspace: the scratch tensor returned by chunk_state(k, v, keep_workspace=True) for the
     same k, v and `segments`; the call then reuses the segment states found there instead of
     reading k, v once more to recompute them (s_final is not available in that case).
+    seg_states: buffer from segment_states_buffer(q, v); a segmented forward stores the state at its
+    segment boundaries there, and causal_dot_product_bwd(..., s_last=..., seg_states=...) then runs
+    the backward as one launch split at those boundaries (few heads per GPU).
     """
     _check_inputs(q, k, v)
     B, H, N, dk = q.shape
@@ -275,6 +292,8 @@ def causal_dot_product_fwd(
         if s_final is not None:
             raise ValueError("flashlinear: s_final cannot be combined with segment_workspace")
         a.segment_states_ready = 1
+    if seg_states is not None:
+        a.seg_states, a.seg_states_bytes = seg_states.data_ptr(), seg_states.numel() * seg_states.element_size()
     _call(0, a, q.device, workspace=segment_workspace)
     _copy_back(out, ov)
     return out
@@ -291,6 +310,7 @@ def causal_dot_product_bwd(
     segments: int = 0,
     s_last: Optional[torch.Tensor] = None,
     keep_padded: bool = False,
+    seg_states: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Gradients (dQ, dK, dV) of causal_dot_product_fwd for upstream gradient `grad_output`.
 
@@ -325,6 +345,8 @@ def causal_dot_product_bwd(
     a.r_final = _fptr(r_final, "r_final", (B * H, dk, dv))
     a.s_last = _fptr(s_last, "s_last", (B * H, dk, dv))
     a.segments = segments
+    if seg_states is not None:
+        a.seg_states, a.seg_states_bytes = seg_states.data_ptr(), seg_states.numel() * seg_states.element_size()
     _call(1, a, q.device)
     for full, view in ((dQ, dQv), (dK, dKv), (dV, dVv)):
         _copy_back(full, view)
@@ -449,15 +471,37 @@ def taylor_features_bwd(dphi: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
 
 
 def backward_uses_final_state(q: torch.Tensor, v: torch.Tensor) -> bool:
-    """True when the backward of this shape runs unsegmented, i.e. can take the forward's final
-    state (`s_last`) and sweep q, k, v, dO once for all three gradients."""
+    """True when the backward of this shape can take the forward's final state (`s_last`) and sweep
+    q, k, v, dO once for all three gradients: it runs unsegmented, or as one launch split at the
+    forward's segment boundaries (then segment_states_buffer() is not None as well)."""
     B, H, N, dk = q.shape
     if dk > KERNEL_HEAD_DIM or v.shape[-1] > KERNEL_HEAD_DIM:
         return False
     a = FlaArgs()
     a.batch, a.heads, a.seqlen, a.dk, a.dv = B, H, N, dk, v.shape[-1]
+    a.debug_flags = _debug_flags
     with torch.cuda.device(q.device):
-        return _lib.load().fla_sm100_auto_segments(ctypes.byref(a), 1) <= 1
+        lib = _lib.load()
+        return lib.fla_sm100_auto_segments(ctypes.byref(a), 1) <= 1 or \
+            lib.fla_sm100_seg_states_bytes(ctypes.byref(a)) > 0
+
+
+def segment_states_buffer(q: torch.Tensor, v: torch.Tensor, segments: int = 0) -> Optional[torch.Tensor]:
+    """Scratch for the states a segmented forward hands to its backward (few heads per GPU), or None
+    when forward + backward of this shape do not use it. Pass it as `seg_states` to
+    causal_dot_product_fwd and causal_dot_product_bwd, together with s_final / s_last."""
+    B, H, N, dk = q.shape
+    if dk > KERNEL_HEAD_DIM or v.shape[-1] > KERNEL_HEAD_DIM:
+        return None
+    a = FlaArgs()
+    a.batch, a.heads, a.seqlen, a.dk, a.dv = B, H, N, dk, v.shape[-1]
+    a.segments = segments
+    a.debug_flags = _debug_flags
+    with torch.cuda.device(q.device):
+        need = _lib.load().fla_sm100_seg_states_bytes(ctypes.byref(a))
+    if need == 0:
+        return None
+    return torch.empty(need, dtype=torch.uint8, device=q.device)
 
 
 def chunk_state(b: torch.Tensor, c: torch.Tensor, segments: int = 0, keep_workspace: bool = False):

@@ -106,10 +106,19 @@ class PeerStateExchange:
     segment states, stores this rank's total into every peer's inbox over NVLink, waits (bounded)
     for the peers' totals and folds the ones that precede (follow) this rank into the segment
     prefixes -- see fla_sm100_state_exchange in include/flashlinear_sm100.h.
-    All ranks must call it the same number of times in the same order."""
+    All ranks must call it the same number of times in the same order.
+
+    A wait that runs out does not stop the step: the kernel sets bit 1 of the device's status word
+    and turns everything it produces into NaN, so the outputs of that step are NaN. Call
+    `ops.check_status(device)` at the next point where the host synchronises anyway (end of a step,
+    before an optimizer update); `close()` does so as well."""
 
     def __init__(self, batch: int, heads: int, dk: int, dv: int, device: torch.device,
-                 group: Optional[dist.ProcessGroup] = None):
+                 group: Optional[dist.ProcessGroup] = None, wait_limit_us: int = 0):
+        # wait_limit_us: how long a block waits for a peer's flag before it gives up (0 = the
+        # library's default of 0.4 s). Ranks that may reach an exchange further apart than that
+        # (first-step compilation, a slow data loader) should raise it.
+        self.wait_limit_us = int(wait_limit_us)
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -163,6 +172,11 @@ class PeerStateExchange:
         """Unmaps the peers' buffers and frees this rank's (call on every rank, after a barrier)."""
         with torch.cuda.device(self.device):
             torch.cuda.synchronize(self.device)
+            failure = None
+            try:
+                ops.check_status(self.device)
+            except RuntimeError as exc:  # report it after the buffers are released
+                failure = exc
             for p in self._opened:
                 self._lib.fla_sm100_exchange_close(p)
             self._opened = []
@@ -171,6 +185,8 @@ class PeerStateExchange:
             for p in self._owned:
                 self._lib.fla_sm100_exchange_free(p)
             self._owned = []
+        if failure is not None:
+            raise failure
 
     def state_and_exchange(self, b: torch.Tensor, c: torch.Tensor, reverse: bool, segments: int = 0):
         """States of this rank's tokens (sum b^T c), exchanged. Returns (workspace, remote, inclusive):
@@ -195,6 +211,7 @@ class PeerStateExchange:
         x = FlaExchange()
         x.rank, x.world, x.reverse, x.epoch = self.rank, self.world, 1 if reverse else 0, 0
         x.epoch_counter = bset["counter"].data_ptr()
+        x.wait_limit_us = self.wait_limit_us
         for r in range(self.world):
             x.inbox[r] = bset["inbox"][r]
             x.flags[r] = bset["flags"][r]

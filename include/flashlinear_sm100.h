@@ -13,7 +13,10 @@
  *  - plain C types only; all tensor pointers are device pointers on the CURRENT device;
  *  - tensors are [batch, heads, seqlen, dim] bf16 with arbitrary (batch, head, token) element
  *    strides and an innermost stride of 1; base addresses and byte strides must be multiples
- *    of 16 (return FLA_ERR_ALIGNMENT otherwise; the Python wrapper then repacks);
+ *    of 16 (return FLA_ERR_ALIGNMENT otherwise; the Python wrapper then repacks); outputs are
+ *    stored in 16-byte units, so the row pitch must cover dim rounded up to a multiple of 8 and,
+ *    when dim is not such a multiple, the elements between a row's last column and the next
+ *    16-byte boundary are overwritten with zeros;
  *  - every call is asynchronous on `stream`, never synchronises, never allocates or frees
  *    device memory; scratch memory (when fla_sm100_workspace_bytes() > 0) is the caller's;
  *  - returns 0 or a negative FLA_ERR_* code for argument errors, synchronously;
@@ -30,7 +33,7 @@
 extern "C" {
 #endif
 
-#define FLA_ABI_VERSION 8
+#define FLA_ABI_VERSION 9
 
 enum {
   FLA_OK = 0,
@@ -98,7 +101,30 @@ typedef struct FlaArgs {
 
   int32_t* status; /* optional device word, see above */
   void* stream;    /* cudaStream_t */
+
+  /* Optional, few heads per GPU: boundary states that a segmented forward stores for the backward.
+   * fla_sm100_seg_states_bytes() says how many bytes the pair of calls wants for these shapes (0:
+   * not used). Give the same buffer, the same `segments` and s_final / s_last to fla_sm100_fwd and
+   * fla_sm100_bwd: the backward then runs as one launch, split at the forward's segment boundaries,
+   * instead of a state pass, a scan and the product pass. The contents are private to the library. */
+  void* seg_states;
+  size_t seg_states_bytes;
+
+  /* Limit of one device-side wait in microseconds (converted with the nominal SM clock);
+   * 0 = the default of about 0.4 s. Legitimate waits of these kernels last microseconds. */
+  uint32_t wait_limit_us;
+  /* FLA_DEBUG_* bits, 0 in production. */
+  uint32_t debug_flags;
 } FlaArgs;
+
+/* Test hook for the status path: the kernel never loads its first tile, so the waits that depend
+ * on it run out after wait_limit_us, bit 0 of *status is set and the CTAs return normally (the
+ * outputs of the call are garbage). Nothing faults or hangs. */
+#define FLA_DEBUG_WITHHOLD_FIRST_TILE 1u
+/* Segmented calls normally run as ONE cooperative launch when all their CTAs fit the GPU at once
+ * (see fla_sm100_seg_states_bytes). This bit keeps the older three-launch form (state pass, scan,
+ * product pass), for comparisons. */
+#define FLA_DEBUG_NO_FUSED_SEGMENTS 2u
 
 /* pass: 0 = forward, 1 = backward, 2 = fla_sm100_state */
 int fla_sm100_abi_version(void);
@@ -106,6 +132,11 @@ const char* fla_sm100_strerror(int code);
 size_t fla_sm100_workspace_bytes(const FlaArgs* args, int pass);
 /* Number of segments the call will use for args->segments == 0. */
 int fla_sm100_auto_segments(const FlaArgs* args, int pass);
+/* Bytes for FlaArgs::seg_states, or 0 when forward + backward of these shapes do not use them (many
+ * heads: nothing is segmented; dk != dv; head dims above 128). The reference has no counterpart: its
+ * grid is (sequence blocks, batch*heads) with quadratic work per block
+ * (flashlinear/kernels/linear_attn_kernels.py:329-331) and needs no state. */
+size_t fla_sm100_seg_states_bytes(const FlaArgs* args);
 
 /* replaces linear_flash_wrapper_fwd / linear_flash_wrapper_fwd_smallv_hd
  * (flashlinear/kernels/linear_attn_kernels.py:310, linear_attn_kernels_smallv_hd.py:320) */
@@ -143,7 +174,13 @@ int fla_sm100_state(const FlaArgs* args, int which);
  * kernel behind it stores that value back; `epoch` is then ignored and the call has no argument
  * that changes between launches, so it can be captured in a CUDA graph and replayed.
  * All ranks must make the same sequence of calls. A peer that never shows up makes the wait run
- * out after about 0.4 s: bit 1 of *status is set and the call's results are invalid. */
+ * out after wait_limit_us (0 = about 0.4 s): bit 1 of *status is set and everything the call
+ * produces (scratch prefixes, remote_out, inclusive_out) is filled with NaN, so that the outputs of
+ * the passes built on it are NaN as well. The wait can also run out when ranks reach the call more
+ * than the limit apart (a slow data loader, a first-call module load): read *status at the next
+ * synchronisation point, or raise the limit. Shapes with more than 592 batch*heads are refused
+ * (FLA_ERR_UNSUPPORTED): every block waits for its twin on the other GPUs, so all blocks must be
+ * resident at once. */
 #define FLA_MAX_RANKS 8
 typedef struct FlaExchange {
   int32_t rank, world;
@@ -154,6 +191,7 @@ typedef struct FlaExchange {
   float* remote_out;    /* optional, fp32 [batch*heads, dk, dv] */
   float* inclusive_out; /* optional, fp32 [batch*heads, dk, dv] */
   uint32_t* epoch_counter; /* optional device word, see above */
+  uint32_t wait_limit_us;  /* how long a block waits for a peer's flag; 0 = 400000 (0.4 s) */
 } FlaExchange;
 /* Bytes of one rank's inbox (*inbox_bytes) and flag array (*flag_bytes) for these shapes. */
 int fla_sm100_exchange_bytes(const FlaArgs* args, int world, size_t* inbox_bytes, size_t* flag_bytes);
@@ -170,8 +208,9 @@ int fla_sm100_exchange_open(const unsigned char* handle64, void** ptr);
 int fla_sm100_exchange_close(void* ptr);
 int fla_sm100_exchange_free(void* ptr);
 /* Lets kernels on the current device store into memory of `peer_device` (cudaDeviceEnablePeerAccess;
- * already-enabled is not an error). Call once per peer before the first exchange: mapping a peer's
- * buffer through CUDA IPC does not by itself make it writable from another device's kernels. */
+ * already-enabled is not an error). Needed for peer memory that was NOT mapped by
+ * fla_sm100_exchange_open (which enables access itself, cudaIpcMemLazyEnablePeerAccess), e.g.
+ * buffers of another device of the same process. */
 int fla_sm100_enable_peer_access(int peer_device);
 
 /* The building block of both passes: o_i = sum_{j<=i} (q_i . k_j) v_j, or with anticausal != 0 the
@@ -243,12 +282,14 @@ int fla_sm100_taylor_features_bwd(const void* dphi, const void* x, void* dx, lon
  * the sequence is split into segments (few heads, long sequences). This variant takes the same
  * FlaArgs (q, k, v, o, optional s_init / s_final, segments, status, stream; workspace fields are
  * ignored) and keeps the per-segment states in a fixed array of FLA_STATIC_SCRATCH_BYTES that is
- * part of the library image on every GPU that loads it.
+ * part of the library image on every GPU that loads it. Shapes that fla_sm100_fwd runs without
+ * scratch (one segment; q/k wider than 128 with v <= 64) are dispatched exactly as it does.
  *  - It performs no device allocation or free, directly or through a library.
  *  - Shapes whose segment states (batch*heads*segments*dk*dv*4 bytes) exceed the array are refused
  *    with FLA_ERR_SCRATCH_LIMIT before anything is launched; pass a smaller `segments`.
- *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
- *    that device current). Make that first call outside any stream capture.
+ *  - The first call on each device THAT SPLITS THE SEQUENCE looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current). Make that first call outside any stream
+ *    capture.
  *  - All calls on a device share the one array. Calls whose kernels may overlap on the GPU (other
  *    streams, other host threads) race on it; serialise them. Nothing in it needs clearing
  *    between calls: each call writes every entry it later reads. */

@@ -29,6 +29,36 @@ def naive_linear_attention(q, k, v, eps: float = 1e-5, normalise: bool = True):
     return out / denom
 
 
+def naive_rows_blocked(q, k, v, dy=None, block: int = 2048):
+    """The same naive path for ONE head ([N, d] tensors), evaluated in blocks of query rows so that
+    the N x N score matrix (flashlinear/test_attn.py:52) never exists as a whole: rows r0..r1 only
+    meet keys 0..r1, exactly what the lower-triangular mask (:54-60) keeps. Returns out, or
+    (out, dq, dk, dv) when `dy` is given: the closed form of what autograd returns for
+    sum(out * dy) (flashlinear/test_attn.py:107-111). Runs in the dtype and on the device of its
+    inputs (float64 for parity checks of long sequences)."""
+    n = q.shape[0]
+    out = torch.empty(n, v.shape[1], dtype=q.dtype, device=q.device)
+    if dy is not None:
+        dq = torch.empty_like(q)
+        dk = torch.zeros_like(k)
+        dv = torch.zeros_like(v)
+    for r0 in range(0, n, block):
+        r1 = min(n, r0 + block)
+        rows = torch.arange(r0, r1, device=q.device).unsqueeze(1)
+        cols = torch.arange(0, r1, device=q.device).unsqueeze(0)
+        mask = cols <= rows
+        p = (q[r0:r1] @ k[:r1].T) * mask
+        out[r0:r1] = p @ v[:r1]
+        if dy is not None:
+            dp = (dy[r0:r1] @ v[:r1].T) * mask
+            dq[r0:r1] = dp @ k[:r1]
+            dk[:r1] += dp.T @ q[r0:r1]
+            dv[:r1] += p.T @ dy[r0:r1]
+    if dy is None:
+        return out
+    return out, dq, dk, dv
+
+
 def time_fwd_bwd_cpu(batch, heads, seqlen, dk, dv, steps=1, warmup=0, threads=None, seed=0, normalise=False):
     """Times forward + autograd backward of the naive path in fp32 on the host cores.
     Returns (seconds per step, threads used)."""
