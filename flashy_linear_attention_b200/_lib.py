@@ -14,7 +14,10 @@ LIB_PATH = os.path.join(_HERE, "libflashlinear_sm100.so")
 FLA_ABI_VERSION = 9
 FLA_DEBUG_WITHHOLD_FIRST_TILE = 1
 FLA_DEBUG_NO_FUSED_SEGMENTS = 2
+FLA_DEBUG_FORCE_SINGLE_SWEEP = 4
 FLA_MAX_RANKS = 8
+FLA_DTYPE_BF16 = 0
+FLA_DTYPE_F16 = 1
 
 
 class FlaTensor(ctypes.Structure):
@@ -54,6 +57,7 @@ class FlaArgs(ctypes.Structure):
         ("stream", ctypes.c_void_p),
         ("seg_states", ctypes.c_void_p),
         ("seg_states_bytes", ctypes.c_size_t),
+        ("dtype", ctypes.c_int32),
         ("wait_limit_us", ctypes.c_uint32),
         ("debug_flags", ctypes.c_uint32),
     ]
@@ -80,6 +84,7 @@ EXPORTED_SYMBOLS = (
     "fla_sm100_workspace_bytes",
     "fla_sm100_auto_segments",
     "fla_sm100_seg_states_bytes",
+    "fla_sm100_bwd_uses_final_state",
     "fla_sm100_fwd",
     "fla_sm100_bwd",
     "fla_sm100_state",
@@ -128,6 +133,8 @@ def load() -> ctypes.CDLL:
     lib.fla_sm100_auto_segments.argtypes = [ctypes.POINTER(FlaArgs), ctypes.c_int]
     lib.fla_sm100_seg_states_bytes.restype = ctypes.c_size_t
     lib.fla_sm100_seg_states_bytes.argtypes = [ctypes.POINTER(FlaArgs)]
+    lib.fla_sm100_bwd_uses_final_state.restype = ctypes.c_int
+    lib.fla_sm100_bwd_uses_final_state.argtypes = [ctypes.POINTER(FlaArgs)]
     lib.fla_sm100_fwd.restype = ctypes.c_int
     lib.fla_sm100_fwd.argtypes = [ctypes.POINTER(FlaArgs)]
     lib.fla_sm100_bwd.restype = ctypes.c_int

@@ -60,6 +60,17 @@ thread_local int g_last_launches = 0;
 thread_local unsigned g_wait_limit_kcycles = 0;
 thread_local int g_debug_withhold = 0;
 thread_local int g_no_fused = 0;  // FLA_DEBUG_NO_FUSED_SEGMENTS: keep the three-launch segmented path
+thread_local int g_force_single_sweep = 0;  // FLA_DEBUG_FORCE_SINGLE_SWEEP
+thread_local int g_half = 0;  // FlaArgs::dtype == FLA_DTYPE_F16
+
+// The single-sweep backward computes dQ as "total minus suffix": every chunk's own share comes out
+// as the difference of two sums over the whole chunk, which costs the early rows of a chunk a few
+// bf16 roundings of accuracy. Over a long sequence that vanishes against the prefix term; over a
+// short one it can push dQ to the reference tests' bound (Frobenius 1e-2 against a bf16 naive
+// path, flashlinear/test_attn.py:17,117). Sequences of at most this many 128-token chunks
+// (the reference's tests stop at 1984 tokens, test_attn.py:69) therefore keep the two-direction form.
+constexpr int kSingleSweepMinChunks = 17;
+bool single_sweep_allowed(int nchunks) { return g_force_single_sweep || nchunks >= kSingleSweepMinChunks; }
 
 // FLA_DEBUG=1 in the environment: failed CUDA calls are described on stderr.
 bool debug_enabled() {
@@ -463,6 +474,12 @@ int device_info(DeviceInfo** out) {
       ok &= cudaFuncSetAttribute(fla::fla_chunk_kernel<128, 128>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  fla::Cfg<128, 128>::SMEM_BYTES) == cudaSuccess;
+      ok &= cudaFuncSetAttribute(fla::fla_chunk_kernel<64, 64, true>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 fla::Cfg<64, 64>::SMEM_BYTES) == cudaSuccess;
+      ok &= cudaFuncSetAttribute(fla::fla_chunk_kernel<128, 128, true>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 fla::Cfg<128, 128>::SMEM_BYTES) == cudaSuccess;
       ok &= cudaFuncSetAttribute(fla::fla_wide_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  fla::WideCfg<2>::SMEM_BYTES) == cudaSuccess;
       ok &= cudaFuncSetAttribute(fla::fla_wide_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -564,9 +581,10 @@ SegPlan backward_aligned_plan(const FlaArgs* a, int sm_count, const SegPlan& f) 
 // calls does not run that way for these shapes.
 size_t seg_states_bytes(const FlaArgs* a, int sm_count, SegPlan* fwd_out, SegPlan* bwd_out) {
   if (a->dk != a->dv || a->dk > 128 || g_no_fused) return 0;
+  if (!single_sweep_allowed((a->seqlen + fla::kChunk - 1) / fla::kChunk)) return 0;
   const int bh = a->batch * a->heads;
   const SegPlan f = forward_plan(a, sm_count);
-  if (f.nseg <= 1 || static_cast<long>(f.nseg) * bh > sm_count) return 0;
+  if (f.nseg <= 1 || static_cast<long>(f.nseg) * bh > sm_count || bh > fla::kBarHeads) return 0;
   const SegPlan b = backward_aligned_plan(a, sm_count, f);
   if (b.nseg <= 1) return 0;
   if (fwd_out) *fwd_out = f;
@@ -579,7 +597,10 @@ int launch_kernel(const KernelParams& kp_in, dim3 grid, cudaStream_t stream) {
   KernelParams kp = kp_in;
   kp.wait_limit_kcycles = g_wait_limit_kcycles;
   kp.debug_withhold = g_debug_withhold;
-  fla::fla_chunk_kernel<D, D><<<grid, fla::kThreads, fla::Cfg<D, D>::SMEM_BYTES, stream>>>(kp);
+  if (g_half)
+    fla::fla_chunk_kernel<D, D, true><<<grid, fla::kThreads, fla::Cfg<D, D>::SMEM_BYTES, stream>>>(kp);
+  else
+    fla::fla_chunk_kernel<D, D><<<grid, fla::kThreads, fla::Cfg<D, D>::SMEM_BYTES, stream>>>(kp);
   ++g_last_launches;
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess)
@@ -614,7 +635,8 @@ int launch_fused_kernel(const KernelParams& kp_in, dim3 grid, cudaStream_t strea
   attr.val.cooperative = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, fla::fla_chunk_kernel<D, D>, kp);
+  const cudaError_t e = g_half ? cudaLaunchKernelEx(&cfg, fla::fla_chunk_kernel<D, D, true>, kp)
+                               : cudaLaunchKernelEx(&cfg, fla::fla_chunk_kernel<D, D, false>, kp);
   ++g_last_launches;
   if (e != cudaSuccess) {
     FLA_LOG_FAILURE("cooperative launch of fla_chunk_kernel<%d> grid (%u,%u,%u) failed: %s", D, grid.x,
@@ -708,7 +730,7 @@ int run_products(const Product* prods, int nprob, int B, int H, int N, int da, i
   // must therefore all carry that state or its transpose (dV and dK: q^T dO and dO^T q) and walk
   // the sequence in the same direction; a product with another state (dQ: v^T k) can only ride
   // along when its starting states come from stored boundary states.
-  bool fusable = !g_no_fused && static_cast<long>(nprob) * nseg * bh <= dev.sm_count;
+  bool fusable = !g_no_fused && static_cast<long>(nprob) * nseg * bh <= dev.sm_count && bh <= fla::kBarHeads;
   {
     const Product* first = nullptr;
     for (int i = 0; i < nprob && fusable; ++i) {
@@ -863,6 +885,7 @@ bool is_wide_c(int da, int dc) { return da <= 128 && dc > 128 && dc <= kWideMaxD
 int run_wide_a(const Product& pd, int B, int H, int N, int da, int dc, int32_t* status,
                cudaStream_t stream) {
   if (!is_wide_a(da, dc)) return FLA_ERR_UNSUPPORTED;
+  if (g_half) return FLA_ERR_UNSUPPORTED;  // the wide-head kernel exists for bf16 only
   if (pd.ext_init != nullptr || pd.ext_final != nullptr) return FLA_ERR_UNSUPPORTED;
   int rc;
   if ((rc = check_operand(pd.a, B, H)) || (rc = check_operand(pd.b, B, H)) ||
@@ -937,6 +960,9 @@ int check_common(const FlaArgs* a, DeviceInfo** dev) {
   }
   g_debug_withhold = (a->debug_flags & FLA_DEBUG_WITHHOLD_FIRST_TILE) ? 1 : 0;
   g_no_fused = (a->debug_flags & FLA_DEBUG_NO_FUSED_SEGMENTS) ? 1 : 0;
+  g_force_single_sweep = (a->debug_flags & FLA_DEBUG_FORCE_SINGLE_SWEEP) ? 1 : 0;
+  if (a->dtype != FLA_DTYPE_BF16 && a->dtype != FLA_DTYPE_F16) return FLA_ERR_INVALID;
+  g_half = a->dtype == FLA_DTYPE_F16 ? 1 : 0;
   return FLA_OK;
 }
 
@@ -1025,11 +1051,24 @@ size_t fla_sm100_workspace_bytes(const FlaArgs* a, int pass) {
 size_t fla_sm100_seg_states_bytes(const FlaArgs* a) {
   if (a == nullptr || a->batch <= 0 || a->heads <= 0 || a->seqlen <= 0) return 0;
   if (a->segment_states_ready) return 0;
-  const int saved = g_no_fused;
+  const int saved = g_no_fused, saved_force = g_force_single_sweep;
   g_no_fused = (a->debug_flags & FLA_DEBUG_NO_FUSED_SEGMENTS) ? 1 : 0;
+  g_force_single_sweep = (a->debug_flags & FLA_DEBUG_FORCE_SINGLE_SWEEP) ? 1 : 0;
   const size_t n = seg_states_bytes(a, current_sm_count_early(), nullptr, nullptr);
   g_no_fused = saved;
+  g_force_single_sweep = saved_force;
   return n;
+}
+
+int fla_sm100_bwd_uses_final_state(const FlaArgs* a) {
+  if (a == nullptr || a->batch <= 0 || a->heads <= 0 || a->seqlen <= 0) return 0;
+  if (a->dk > 128 || a->dv > 128) return 0;
+  const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
+  if (!(nchunks >= kSingleSweepMinChunks || (a->debug_flags & FLA_DEBUG_FORCE_SINGLE_SWEEP))) return 0;
+  if (fla_sm100_seg_states_bytes(a) > 0) return 1;
+  int nseg = a->segments > 0 ? a->segments
+                             : auto_segments(3, a->batch * a->heads, nchunks, current_sm_count_early());
+  return nseg <= 1 ? 1 : 0;
 }
 
 int fla_sm100_fwd(const FlaArgs* a) {
@@ -1109,7 +1148,7 @@ int fla_sm100_bwd(const FlaArgs* a) {
     return rc;
   }
   const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
-  if (a->seg_states != nullptr && a->s_last != nullptr) {
+  if (a->seg_states != nullptr && a->s_last != nullptr && single_sweep_allowed(nchunks)) {
     // Few heads: the forward ran as one fused segmented launch and stored the state at each of
     // its segment boundaries. The backward is split at a subset of those boundaries; dQ walks every
     // segment end-to-start from the stored state at the segment's end (total minus suffix, as in
@@ -1135,7 +1174,7 @@ int fla_sm100_bwd(const FlaArgs* a) {
   int nseg = a->segments > 0 ? a->segments
                              : auto_segments(3, a->batch * a->heads, nchunks, dev->sm_count);
   if (nseg > nchunks) nseg = nchunks;
-  if (a->s_last != nullptr && nseg <= 1) {
+  if (a->s_last != nullptr && nseg <= 1 && single_sweep_allowed(nchunks)) {
     // The forward state after this call's tokens is known: dQ can walk the sequence in the same
     // descending order as dV and dK (state = total minus suffix), so the three products of a
     // head stream the same chunks at the same time and share their q, k, v, dO reads in L2.

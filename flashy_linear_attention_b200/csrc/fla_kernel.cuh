@@ -89,21 +89,26 @@ struct KernelParams {
   // Every CTA first sums b^T c over its share of the chunks of its segment (phase A; operands and
   // walking direction of problem `pre_prob`; the `gridDim.x` CTAs of a (segment, head) split the
   // segment's chunks between them) and stores the sum as partial (segment * gridDim.x + blockIdx.x)
-  // of its head in part_out. All CTAs then meet at a grid-wide barrier (the launch must be
-  // cooperative: every CTA resident), after which each CTA adds up the partials of the segments
-  // before its own, takes that as its starting state and runs the attention loop. The last
-  // segment's own sum is never needed and is skipped.
+  // of its head in part_out. The CTAs of a head then meet at a barrier (the launch must be
+  // cooperative: every CTA resident), turn the partials into per-segment prefixes together (each
+  // CTA scans a slice of the state's elements over all segments, in place: the prefix of segment
+  // s lands in slot s * gridDim.x), meet again, and each CTA takes the prefix of its segment as
+  // its starting state and runs the attention loop. The last segment's own sum is never needed
+  // and is skipped.
   int fused;
   int pre_prob;
   float* part_out;
   unsigned bar_slot;   // which pair of g_grid_barriers this launch uses
 };
 
-// Barrier words of the fused form: kGridBarSlots pairs (arrival count, generation), zero when the
-// module is loaded and left zero / consistent by every launch (see ptx::grid_barrier). The host
-// hands out the slots round-robin, so launches that may overlap on the GPU use different pairs.
+// Barrier words of the fused form. Only the CTAs of one head exchange data, so every head has its
+// own two barriers (after the partial sums, after the scan): [launch slot][head][barrier] pairs of
+// (arrival count, generation), zero when the module is loaded and left consistent by every launch
+// (see ptx::grid_barrier). The host hands out the launch slots round-robin, so launches that may
+// overlap on the GPU use different words.
 constexpr int kGridBarSlots = 64;
-static __device__ unsigned g_grid_barriers[2 * kGridBarSlots];
+constexpr int kBarHeads = 80;  // the fused form needs heads * segments * products <= SM count anyway
+static __device__ unsigned g_grid_barriers[kGridBarSlots * kBarHeads * 2 * 2];
 
 template <int DK, int DV>
 struct Cfg {
@@ -126,13 +131,338 @@ struct Cfg {
   // TMEM columns (32-bit each, 128 lanes)
   static constexpr int P_COL = 0;         // P fp32: 128 columns
   static constexpr int PB_COL = 128;      // P bf16 (two per column): two buffers of 64 columns
-  static constexpr int O_COL = 256;       // O fp32: DV columns
-  static constexpr int S_COL = 256 + DV;  // S fp32: DV columns, lane = dk index
+  // O fp32: DV columns per buffer. With DV <= 64 there is room for two accumulators, so issuer Y
+  // starts chunk i + 1 while the epilogue still reads chunk i; with DV = 128 tensor memory is full
+  // and the accumulator is single.
+  static constexpr int O_BUFS = (DV <= 64) ? 2 : 1;
+  static constexpr int O_COL = 256;
+  static constexpr int S_COL = 256 + O_BUFS * DV;  // S fp32: DV columns, lane = dk index
   static constexpr int TMEM_COLS = 512;
   static_assert(S_COL + DV <= TMEM_COLS, "TMEM budget");
 };
 
-template <int DK, int DV>
+// Arguments of converter_prologue(): where the CTA is and where its buffers and barriers are.
+struct PrologueArgs {
+  int prob_idx, g, nseg, bh, a_iter;
+  uint32_t tmem_base, sb_addr, ost_addr;
+  uint32_t s_full, part_done, grid_done, sb_ready;  // mbarrier addresses
+  volatile int* abort_flag;
+};
+
+// What the converter warps (2..9) do before the chunk loop. Fused form: store the partial sum of
+// phase A, meet the head's other CTAs, scan, meet again. Then, whenever the CTA starts from a
+// state: fetch it, write it to TMEM (fp32) and to the operand buffer (16-bit) and release the MMA
+// issuers. Returns false when a bounded wait gave up.
+template <int DK, int DV, bool HALF>
+__device__ __noinline__ bool converter_prologue(const KernelParams& p, const PrologueArgs pa) {
+  using cfg = Cfg<DK, DV>;
+  const int warp = static_cast<int>(threadIdx.x >> 5);
+  const int lane = static_cast<int>(threadIdx.x & 31);
+  const int g = pa.g, nseg = pa.nseg, bh = pa.bh, a_iter = pa.a_iter;
+  // Copies of the parameters this function reads inside its loops: `p` is a generic reference here,
+  // and the L2 loads below are volatile with memory clobbers, so a p.x in a loop would be fetched
+  // again after every one of them.
+  const Problem& pr = p.prob[pa.prob_idx];
+  const int st_rows = p.st_rows, st_cols = p.st_cols, seg_chunks = p.seg_chunks;
+  float* const part_out = p.part_out;
+  const unsigned bar_slot = p.bar_slot % kGridBarSlots;
+  float* const bound_out = pr.bound_out;
+  const bool fused = p.fused != 0;
+  const bool has_init = fused || pr.s_init != nullptr;
+  const uint32_t sb_addr = pa.sb_addr, ost_addr = pa.ost_addr;
+  const uint32_t s_full = pa.s_full, part_done = pa.part_done, grid_done = pa.grid_done, sb_ready = pa.sb_ready;
+  volatile int* abort_flag = pa.abort_flag;
+  const size_t st_elems = static_cast<size_t>(st_rows) * st_cols;
+  const size_t st_index = (fused ? static_cast<size_t>(bh) : static_cast<size_t>(bh) * nseg + g) * st_elems;
+  const bool st_trans = pr.st_trans != 0;
+  const int half = (warp - 2) >> 2;
+  const int quad = warp & 3;
+  const int row = quad * 32 + lane;
+  const uint32_t lane_base = pa.tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+  const uint32_t sb_row = sb_addr + row * 128;
+  const uint32_t swz = static_cast<uint32_t>(row & 7);
+  constexpr int SBLK = DV / 64;
+  constexpr bool kStagedStateIO = (DK == 128);
+  const uint32_t xpose_off = static_cast<uint32_t>(warp - 2) * 4096u;
+  uint32_t ra[32], rb[32];
+  auto wait_uniform = [&](uint32_t bar, uint32_t parity) {
+    const int ok = ptx::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+    return __all_sync(0xffffffffu, ok) != 0;
+  };
+  auto xpose_addr = [&](uint32_t base, int j, int r) {
+    return base + xpose_off + static_cast<uint32_t>((j * 32 + (r ^ j)) * 4);
+  };
+  auto store_sb = [&](int cb, const uint32_t (&r)[32]) {
+    const uint32_t grp = sb_row + (cb >> 1) * (DK * 128);
+    const uint32_t j0 = (cb & 1) * 4;
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      const uint32_t a0 = ptx::pack16x2<HALF>(__uint_as_float(r[jj * 8 + 0]), __uint_as_float(r[jj * 8 + 1]));
+      const uint32_t a1 = ptx::pack16x2<HALF>(__uint_as_float(r[jj * 8 + 2]), __uint_as_float(r[jj * 8 + 3]));
+      const uint32_t a2 = ptx::pack16x2<HALF>(__uint_as_float(r[jj * 8 + 4]), __uint_as_float(r[jj * 8 + 5]));
+      const uint32_t a3 = ptx::pack16x2<HALF>(__uint_as_float(r[jj * 8 + 6]), __uint_as_float(r[jj * 8 + 7]));
+      ptx::st_shared_v4(grp + (((j0 + jj) ^ swz) << 4), a0, a1, a2, a3);
+    }
+  };
+
+    bool conv_ok = true;
+  unsigned gen0 = 0, gen1 = 0;  // barrier generations, fetched while phase A still runs
+  if (fused && warp == 2 && lane == 0) {
+    gen0 = ptx::barrier_generation(&g_grid_barriers[((bar_slot * kBarHeads + bh) * 2 + 0) * 2]);
+    gen1 = ptx::barrier_generation(&g_grid_barriers[((bar_slot * kBarHeads + bh) * 2 + 1) * 2]);
+  }
+  if (fused) {
+    // ---------------- phase A read-out: this CTA's partial sum -> part_out (scratch layout,
+    // one thread per state row), then the barrier of the head's CTAs. Every CTA takes part in
+    // the barriers, whether it had chunks to sum or not.
+    if (a_iter > 0) {
+      int ok = ptx::mbar_wait(s_full, 0, abort_flag) ? 1 : 0;
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        ptx::tc_fence_after();
+        const size_t slot = static_cast<size_t>(bh) * (static_cast<size_t>(nseg) * gridDim.x) +
+                            static_cast<size_t>(g) * gridDim.x + blockIdx.x;
+        float* dst = part_out + slot * st_elems;
+#pragma unroll 1
+        for (int jb = 0; jb < SBLK; ++jb) {
+          const int cb = half * SBLK + jb;
+          ptx::tmem_ld32(lane_base + cfg::S_COL + cb * 32, ra);
+          if (row < st_rows) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (cb * 32 + j < st_cols)
+                __stcg(dst + static_cast<size_t>(cb * 32 + j) * st_rows + row, __uint_as_float(ra[j]));
+          }
+        }
+        ptx::tc_fence_before();
+      }
+      conv_ok = ok != 0;
+    }
+    // Barrier of this head's CTAs: every converter thread fences its stores and reports on an
+    // mbarrier; one warp then arrives at the head's barrier word, waits for the other CTAs of
+    // the head and releases the group. Used twice (after the partials, after the scan).
+    const unsigned head_ctas = gridDim.x * gridDim.y;
+    auto head_bar_words = [&](int which) {
+      return &g_grid_barriers[((bar_slot * kBarHeads + bh) * 2 + which) * 2];
+    };
+    auto head_barrier = [&](int which, unsigned gen_before) {
+      __threadfence();
+      if (conv_ok) ptx::mbar_arrive(part_done);
+      if (warp == 2) {
+        bool ok = wait_uniform(part_done, which);
+        if (ok) {
+          int passed = 1;
+          if (lane == 0)
+            passed = ptx::grid_barrier(head_bar_words(which), head_ctas, gen_before, abort_flag) ? 1 : 0;
+          ok = __shfl_sync(0xffffffffu, passed, 0) != 0;
+        }
+        if (ok && lane == 0) ptx::mbar_arrive(grid_done);
+      }
+      if (conv_ok) {
+        const int ok = ptx::mbar_wait(grid_done, which, abort_flag) ? 1 : 0;
+        conv_ok = __all_sync(0xffffffffu, ok) != 0;
+      }
+    };
+    head_barrier(0, gen0);
+    if (conv_ok && nseg > 1) {
+      // ---------------- scan: partial sums -> exclusive prefixes per segment, in place. This CTA
+      // owns one slice of the state's elements for ALL segments of its head. Slots are walked in
+      // order (slot j = segment j / nsplit, share j % nsplit); after the last share of segment
+      // s the running sum is the prefix of segment s + 1 and overwrites slot (s + 1) * nsplit.
+      // kScanSlots slots of kScanElems elements are loaded at a time, all loads before the first
+      // use; a prefix whose slot is the first one of the NEXT batch is written only after that
+      // batch has been loaded (its partial is still needed).
+      constexpr int kScanSlots = 8, kScanElems = 4;
+      const int nsplit = static_cast<int>(gridDim.x);
+      const int elems = static_cast<int>(st_elems);
+      const int slice = (elems + static_cast<int>(head_ctas) - 1) / static_cast<int>(head_ctas);
+      const int lo = (g * nsplit + static_cast<int>(blockIdx.x)) * slice;
+      const int hi = min(elems, lo + slice);
+      const int tid = (warp - 2) * 32 + lane;
+      float* hb = part_out + static_cast<size_t>(bh) * (static_cast<size_t>(nseg) * nsplit) * st_elems;
+      const int nslots = (nseg - 1) * nsplit;  // slots that can hold a partial
+      // bit x: share x of a segment is not empty (a CTA with an empty share stored nothing)
+      unsigned stored_mask = 0;
+      for (int x = 0; x < nsplit; ++x)
+        if (seg_chunks * (x + 1) / nsplit - seg_chunks * x / nsplit > 0) stored_mask |= 1u << x;
+#pragma unroll 1
+      for (int e0 = lo + tid; e0 < hi; e0 += 256 * kScanElems) {
+        float run[kScanElems], pending[kScanElems];
+#pragma unroll
+        for (int u = 0; u < kScanElems; ++u) run[u] = 0.f;
+        bool have_pending = false;
+        int x0 = 0;  // share index of slot j0
+#pragma unroll 1
+        for (int j0 = 0; j0 < nslots; j0 += kScanSlots) {
+          uint32_t val[kScanElems * kScanSlots];
+          static_assert(kScanElems * kScanSlots == 32, "one keep_together() per batch");
+#pragma unroll
+          for (int u = 0; u < kScanElems; ++u) {
+            const int e = e0 + 256 * u;
+#pragma unroll
+            for (int jj = 0; jj < kScanSlots; ++jj) {
+              const int j = j0 + jj;
+              const bool want = e < hi && j < nslots;
+              val[u * kScanSlots + jj] =
+                  ptx::ld_global_cg_b32(hb + (want ? static_cast<size_t>(j) * st_elems + e : 0));
+            }
+          }
+          ptx::keep_together(val);  // all loads of the batch before any store
+          if (have_pending) {       // prefix held back by the batch before: its slot is j0
+#pragma unroll
+            for (int u = 0; u < kScanElems; ++u)
+              if (e0 + 256 * u < hi) __stcg(hb + static_cast<size_t>(j0) * st_elems + e0 + 256 * u, pending[u]);
+            have_pending = false;
+          }
+          int x = x0;
+#pragma unroll
+          for (int jj = 0; jj < kScanSlots; ++jj) {
+            const int j = j0 + jj;
+            if (j < nslots) {
+              const bool add = (stored_mask >> x) & 1u;
+              const bool seg_end = x + 1 == nsplit;
+              // the prefix goes to slot j + 1; if that is the first slot of the next batch, later
+              const bool defer = jj == kScanSlots - 1 && j + 1 < nslots;
+#pragma unroll
+              for (int u = 0; u < kScanElems; ++u) {
+                if (add) run[u] += __uint_as_float(val[u * kScanSlots + jj]);
+                if (seg_end) {
+                  if (defer) pending[u] = run[u];
+                  else if (e0 + 256 * u < hi)
+                    __stcg(hb + static_cast<size_t>(j + 1) * st_elems + e0 + 256 * u, run[u]);
+                }
+              }
+              if (seg_end && defer) have_pending = true;
+              x = seg_end ? 0 : x + 1;
+            }
+          }
+          x0 = x;
+        }
+      }
+    }
+    head_barrier(1, gen1);
+  }
+
+  if (has_init && conv_ok) {
+    // ---------------- phase B: the state this CTA starts from -> TMEM (fp32) and the bf16
+    // operand buffer: an optional array of the caller plus `nsrc` arrays `stride` elements apart
+    // (the segment's stored state; partial sums of earlier segments; one stored boundary state).
+    //
+    // fetch(): one 32-column block of a [st_rows][st_cols] array (transposed storage if `trans`)
+    // into a register array, zero outside the valid part. All 32 loads are issued before their
+    // first use (volatile loads keep their order), so every thread has 32 requests in flight:
+    // the arrays sit in L2 (loads bypass L1: in the fused form other CTAs of the same launch wrote
+    // them) and the step is pure latency otherwise. Row-major arrays are fetched along rows by
+    // the lanes (whole 128-byte segments per warp instruction) and settle() then exchanges them
+    // through the output staging buffer, which is idle before chunk 0.
+    auto fetch = [&](int cb, const float* base, bool trans, uint32_t (&r)[32]) {
+      if (kStagedStateIO && !trans) {
+        const int col = cb * 32 + lane;
+#pragma unroll
+        for (int rr = 0; rr < 32; ++rr) {
+          const int grow = quad * 32 + rr;
+          const bool valid = col < st_cols && grow < st_rows;
+          r[rr] = ptx::ld_global_cg_b32(base + (valid ? static_cast<size_t>(grow) * st_cols + col : 0));
+        }
+        ptx::keep_together(r);
+#pragma unroll
+        for (int rr = 0; rr < 32; ++rr)
+          if (!(col < st_cols && quad * 32 + rr < st_rows)) r[rr] = 0u;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = cb * 32 + j;
+          const bool valid = row < st_rows && col < st_cols;
+          const size_t off = trans ? static_cast<size_t>(col) * st_rows + row
+                                   : static_cast<size_t>(row) * st_cols + col;
+          r[j] = ptx::ld_global_cg_b32(base + (valid ? off : 0));
+        }
+        ptx::keep_together(r);
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (!(row < st_rows && cb * 32 + j < st_cols)) r[j] = 0u;
+      }
+    };
+    auto settle = [&](bool trans, uint32_t (&r)[32]) {
+      if (kStagedStateIO && !trans) {
+        const uint32_t base = ost_addr;
+#pragma unroll
+        for (int rr = 0; rr < 32; ++rr) ptx::st_shared_b32(xpose_addr(base, lane, rr), r[rr]);
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = ptx::ld_shared_b32(xpose_addr(base, j, lane));
+        __syncwarp();
+      }
+    };
+    const float* add = nullptr;   // caller's state
+    const float* src = nullptr;   // first of the nsrc arrays
+    bool add_trans = pr.add_trans != 0, src_trans = false;
+    size_t stride = 0;
+    int nsrc = 0;
+    const size_t head_index = static_cast<size_t>(bh) * st_elems;
+    if (!fused) {
+      src = pr.s_init + st_index;
+      src_trans = st_trans;
+      nsrc = 1;
+      if (pr.s_add != nullptr) add = pr.s_add + head_index;
+    } else {
+      // caller's state: every segment for kInitParts, the first one only for kInitBound
+      const bool bound = pr.init_kind == kInitBound;
+      if (pr.s_add != nullptr && (!bound || g == 0)) add = pr.s_add + head_index;
+      src_trans = pr.init_trans != 0;
+      stride = st_elems;
+      if (bound) {
+        const size_t slot = static_cast<size_t>(bh) * pr.init_stride + (pr.bound_slot0 - g * pr.bound_step);
+        src = pr.init_base + slot * st_elems;
+        nsrc = g > 0 ? 1 : 0;
+      } else {
+        // the scanned prefix of this segment (slot g * nsplit of the head); segment 0 has none
+        const int slots = static_cast<int>(gridDim.x);
+        src = pr.init_base + (static_cast<size_t>(bh) * (static_cast<size_t>(nseg) * slots) +
+                              static_cast<size_t>(g) * slots) * st_elems;
+        nsrc = g > 0 ? 1 : 0;
+      }
+    }
+#pragma unroll 1
+    for (int jb = 0; jb < SBLK; ++jb) {
+      const int cb = half * SBLK + jb;
+      if (add != nullptr) {
+        fetch(cb, add, add_trans, ra);
+        settle(add_trans, ra);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) ra[j] = 0u;
+      }
+#pragma unroll 1
+      for (int j = 0; j < nsrc; ++j) {
+        fetch(cb, src + j * stride, src_trans, rb);
+        settle(src_trans, rb);
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          ra[c] = __float_as_uint(__uint_as_float(ra[c]) + __uint_as_float(rb[c]));
+      }
+      if (fused && bound_out != nullptr && g > 0 && row < st_rows) {
+        float* dst = bound_out + (static_cast<size_t>(bh) * (nseg - 1) + (g - 1)) * st_elems;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (cb * 32 + j < st_cols)
+            __stcg(dst + static_cast<size_t>(cb * 32 + j) * st_rows + row, __uint_as_float(ra[j]));
+      }
+      ptx::tmem_st32(lane_base + cfg::S_COL + cb * 32, ra);
+      if (row < DK) store_sb(cb, ra);
+    }
+    ptx::tc_wait_st();
+    ptx::fence_proxy_async_smem();
+    ptx::tc_fence_before();
+    ptx::mbar_arrive(sb_ready);
+  }
+
+  return conv_ok;
+}
+
+// HALF: operands and outputs are fp16 instead of bf16 (same tiles, same pipeline; only the MMA
+// operand format and the fp32 -> 16-bit roundings differ).
+template <int DK, int DV, bool HALF = false>
 __global__ void __launch_bounds__(kThreads, 1)
 fla_chunk_kernel(const __grid_constant__ KernelParams p) {
   using cfg = Cfg<DK, DV>;
@@ -166,7 +496,9 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
   const uint32_t qs_done = bar_base + 8u * (2 * NSLOT + 6);
   const uint32_t p_read = bar_base + 8u * (2 * NSLOT + 8);
   const uint32_t sb_ready = bar_base + 8u * (2 * NSLOT + 3);
-  const uint32_t o_free = bar_base + 8u * (2 * NSLOT + 5);
+  // one o_free barrier per accumulator buffer (both names denote the same barrier when there is one)
+  const uint32_t o_free0 = bar_base + 8u * (2 * NSLOT + 5);
+  const uint32_t o_free1 = cfg::O_BUFS == 2 ? bar_base + 8u * (2 * NSLOT + 9) : o_free0;
   const uint32_t s_full = bar_base + 8u * (2 * NSLOT + 4);
   const uint32_t part_done = bar_base + 8u * (2 * NSLOT + 10);  // fused: partial sum stored (256 arrivals)
   const uint32_t grid_done = bar_base + 8u * (2 * NSLOT + 11);  // fused: the grid barrier was passed
@@ -229,7 +561,8 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
     ptx::mbar_init(qs_done, 1);
     ptx::mbar_init(p_read, 256);
     ptx::mbar_init(sb_ready, 256);
-    ptx::mbar_init(o_free, 128);
+    ptx::mbar_init(o_free0, 128);
+    if (cfg::O_BUFS == 2) ptx::mbar_init(o_free1, 128);
     ptx::mbar_init(s_full, 1);
     ptx::mbar_init(part_done, 256);
     ptx::mbar_init(grid_done, 1);
@@ -316,8 +649,8 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
     //   p_read(i)      the converters have read P of chunk i out of TMEM        (before P = ..)
     //   o_full(i-1)    issuer Y's P V of chunk i-1 is done: that bf16 P buffer is reused by
     //                  the conversion of the tile written here
-    constexpr uint32_t IDESC_QK = ptx::make_idesc(128, kChunk, false, false);  // P  = Q K^T
-    constexpr uint32_t IDESC_KV_ADD = ptx::make_idesc(128, DV, true, true);    // S += K^T V
+    constexpr uint32_t IDESC_QK = ptx::make_idesc(128, kChunk, false, false, HALF);  // P  = Q K^T
+    constexpr uint32_t IDESC_KV_ADD = ptx::make_idesc(128, DV, true, true, HALF);    // S += K^T V
     constexpr uint32_t IDESC_KV_SUB = IDESC_KV_ADD | (1u << 13);               // S -= K^T V (A negated)
     const uint32_t IDESC_KV = tms ? IDESC_KV_SUB : IDESC_KV_ADD;
     const uint32_t tP = tmem_base + cfg::P_COL;
@@ -424,14 +757,15 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
   } else if (warp == 14) {
     // ================================================================ MMA issuer Y
     // O = Q_i Sb_{i-1}, then O += Pb_i V_i. Edges besides tile arrival:
-    //   o_free(i-1)   the epilogue has drained the accumulator of chunk i-1
+    //   o_free(i-1)   the epilogue has drained the accumulator of chunk i-1 (of chunk i-2 when
+    //                 there are two accumulators)
     //   sb_ready(i-1) the bf16 state of chunk i-1 is in shared memory
     //   pb_ready(i)   the bf16 score tile of chunk i is in TMEM
     // and it signals qs_done(i) (the state buffer may be overwritten) and o_full(i).
     if (mode == 0) {
-      constexpr uint32_t IDESC_PV = ptx::make_idesc(128, DV, false, true);  // O += Pb V
-      constexpr uint32_t IDESC_QS = ptx::make_idesc(128, DV, false, true);  // O  = Q Sb
-      const uint32_t tO = tmem_base + cfg::O_COL;
+      constexpr uint32_t IDESC_PV = ptx::make_idesc(128, DV, false, true, HALF);  // O += Pb V
+      constexpr uint32_t IDESC_QS = ptx::make_idesc(128, DV, false, true, HALF);  // O  = Q Sb
+      const uint32_t tO0 = tmem_base + cfg::O_COL;
       const uint32_t sb_lo = ptx::desc_lo(sb_addr, DK * 128);  // MN-major, groups DK*128 B apart
       const bool leader = ptx::elect_one();
       auto wait_tile = [&](int t) { return wait_uniform(full_bar(t % NSLOT), (t / NSLOT) & 1); };
@@ -442,7 +776,12 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
         const bool have_state = (i > 0) || has_init;
         const bool use_state = have_state && !plain_chunk(i);
         const uint32_t tPb = tmem_base + cfg::PB_COL + (i & 1) * 64;
-        if (i >= 1 && !wait_uniform(o_free, (i - 1) & 1)) break;
+        const uint32_t tO = tO0 + (cfg::O_BUFS == 2 ? (i & 1) * DV : 0);
+        if (cfg::O_BUFS == 2) {
+          if (i >= 2 && !wait_uniform((i & 1) ? o_free1 : o_free0, ((i - 2) >> 1) & 1)) break;
+        } else {
+          if (i >= 1 && !wait_uniform(o_free0, (i - 1) & 1)) break;
+        }
         if (have_state) {
           if (!wait_uniform(sb_ready, sb_waits & 1)) break;
           ++sb_waits;
@@ -494,10 +833,10 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       const uint32_t j0 = (cb & 1) * 4;
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) {
-        const uint32_t a0 = ptx::pack_bf16x2(__uint_as_float(r[jj * 8 + 0]), __uint_as_float(r[jj * 8 + 1]));
-        const uint32_t a1 = ptx::pack_bf16x2(__uint_as_float(r[jj * 8 + 2]), __uint_as_float(r[jj * 8 + 3]));
-        const uint32_t a2 = ptx::pack_bf16x2(__uint_as_float(r[jj * 8 + 4]), __uint_as_float(r[jj * 8 + 5]));
-        const uint32_t a3 = ptx::pack_bf16x2(__uint_as_float(r[jj * 8 + 6]), __uint_as_float(r[jj * 8 + 7]));
+        const uint32_t a0 = ptx::pack16x2<HALF>(__uint_as_float(r[jj * 8 + 0]), __uint_as_float(r[jj * 8 + 1]));
+        const uint32_t a1 = ptx::pack16x2<HALF>(__uint_as_float(r[jj * 8 + 2]), __uint_as_float(r[jj * 8 + 3]));
+        const uint32_t a2 = ptx::pack16x2<HALF>(__uint_as_float(r[jj * 8 + 4]), __uint_as_float(r[jj * 8 + 5]));
+        const uint32_t a3 = ptx::pack16x2<HALF>(__uint_as_float(r[jj * 8 + 6]), __uint_as_float(r[jj * 8 + 7]));
         ptx::st_shared_v4(grp + (((j0 + jj) ^ swz) << 4), a0, a1, a2, a3);
       }
     };
@@ -536,172 +875,35 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
     // Reads this group's share of S from TMEM and routes it to the operand buffer and/or s_final.
     auto convert_state = [&](bool to_sb, bool to_final) {
       if (SBLK == 2) {
-        ptx::tmem_ld32(lane_base + cfg::S_COL + (half * 2) * 32, ra);
-        ptx::tmem_ld32(lane_base + cfg::S_COL + (half * 2 + 1) * 32, rb);
-        ptx::tc_wait_ld();
+        ptx::tmem_ld32x2(lane_base + cfg::S_COL + (half * 2) * 32, ra,
+                         lane_base + cfg::S_COL + (half * 2 + 1) * 32, rb);
         if (to_final) { write_final(half * 2, ra); write_final(half * 2 + 1, rb); }
         if (to_sb && row < DK) { store_sb(half * 2, ra); store_sb(half * 2 + 1, rb); }
       } else {
         ptx::tmem_ld32(lane_base + cfg::S_COL + half * 32, ra);
-        ptx::tc_wait_ld();
         if (to_final) write_final(half, ra);
         if (to_sb && row < DK) store_sb(half, ra);
       }
     };
 
-    bool conv_ok = true;
-    if (fused) {
-      // ---------------- phase A read-out: this CTA's partial sum -> part_out (scratch layout,
-      // one thread per state row), then the grid-wide barrier. Every CTA of the grid takes part
-      // in the barrier, whether it had chunks to sum or not.
-      if (a_iter > 0) {
-        int ok = ptx::mbar_wait(s_full, 0, abort_flag) ? 1 : 0;
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-          ptx::tc_fence_after();
-          const size_t slot = static_cast<size_t>(bh) * (static_cast<size_t>(nseg) * gridDim.x) +
-                              static_cast<size_t>(g) * gridDim.x + blockIdx.x;
-          float* dst = p.part_out + slot * st_elems;
-#pragma unroll 1
-          for (int jb = 0; jb < SBLK; ++jb) {
-            const int cb = half * SBLK + jb;
-            ptx::tmem_ld32(lane_base + cfg::S_COL + cb * 32, ra);
-            ptx::tc_wait_ld();
-            if (row < p.st_rows) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (cb * 32 + j < p.st_cols)
-                  __stcg(dst + static_cast<size_t>(cb * 32 + j) * p.st_rows + row, __uint_as_float(ra[j]));
-            }
-          }
-          ptx::tc_fence_before();
-        }
-        conv_ok = ok != 0;
-      }
-      __threadfence();  // the partial sum is visible device-wide before this thread reports it stored
-      if (conv_ok) ptx::mbar_arrive(part_done);
-      if (warp == 2) {
-        // One warp per CTA arrives at the grid barrier once all 256 converter threads have stored
-        // (and fenced) their share, waits for the other CTAs, and releases the rest of the group.
-        bool ok = wait_uniform(part_done, 0);
-        if (ok) {
-          int passed = 1;
-          if (lane == 0) passed = ptx::grid_barrier(&g_grid_barriers[2 * (p.bar_slot % kGridBarSlots)],
-                                             gridDim.x * gridDim.y * gridDim.z, abort_flag) ? 1 : 0;
-          ok = __shfl_sync(0xffffffffu, passed, 0) != 0;
-        }
-        if (ok && lane == 0) ptx::mbar_arrive(grid_done);
-      }
-      if (conv_ok) {
-        int ok = ptx::mbar_wait(grid_done, 0, abort_flag) ? 1 : 0;
-        conv_ok = __all_sync(0xffffffffu, ok) != 0;
-      }
-    }
-
-    if (has_init && conv_ok) {
-      // One 32-column block of a [st_rows][st_cols] state array (transposed storage if `trans`)
-      // into this thread's row registers; zero outside the valid part. Loads bypass L1: in the
-      // fused form the arrays were written by other CTAs of this launch.
-      auto load_block = [&](int cb, const float* ptr, size_t index0, bool trans, uint32_t (&out)[32]) {
-        if (kStagedStateIO && !trans) {
-          const uint32_t base = ost_addr;  // the output staging buffer is idle before chunk 0
-          const int col = cb * 32 + lane;
-#pragma unroll 4
-          for (int rr = 0; rr < 32; ++rr) {
-            const int grow = quad * 32 + rr;
-            float x = 0.f;
-            if (grow < p.st_rows && col < p.st_cols)
-              x = __ldcg(ptr + index0 + static_cast<size_t>(grow) * p.st_cols + col);
-            ptx::st_shared_b32(xpose_addr(base, lane, rr), __float_as_uint(x));
-          }
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) out[j] = ptx::ld_shared_b32(xpose_addr(base, j, lane));
-          __syncwarp();
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int col = cb * 32 + j;
-            float x = 0.f;
-            if (row < p.st_rows && col < p.st_cols)
-              x = __ldcg(ptr + index0 + (trans ? static_cast<size_t>(col) * p.st_rows + row
-                                               : static_cast<size_t>(row) * p.st_cols + col));
-            out[j] = __float_as_uint(x);
-          }
-        }
-      };
-      auto accumulate = [&](const uint32_t (&x)[32]) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          ra[j] = __float_as_uint(__uint_as_float(ra[j]) + __uint_as_float(x[j]));
-      };
-      const size_t head_index = static_cast<size_t>(bh) * st_elems;
-#pragma unroll 1
-      for (int jb = 0; jb < SBLK; ++jb) {
-        const int cb = half * SBLK + jb;
-        if (!fused) {
-          load_block(cb, pr.s_init, st_index, st_trans, ra);
-          if (pr.s_add != nullptr) {
-            load_block(cb, pr.s_add, head_index, pr.add_trans != 0, rb);
-            accumulate(rb);
-          }
-        } else {
-          // caller's state (every segment for kInitParts, the first one only for kInitBound)
-          const bool bound = pr.init_kind == kInitBound;
-          if (pr.s_add != nullptr && (!bound || g == 0)) {
-            load_block(cb, pr.s_add, head_index, pr.add_trans != 0, ra);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) ra[j] = 0u;
-          }
-          const bool itrans = pr.init_trans != 0;
-          if (bound) {
-            if (g > 0) {
-              const size_t slot = static_cast<size_t>(bh) * pr.init_stride + (pr.bound_slot0 - g * pr.bound_step);
-              load_block(cb, pr.init_base, slot * st_elems, itrans, rb);
-              accumulate(rb);
-            }
-          } else {
-            // partial sums of all earlier segments, two in flight at a time
-            const int nsplit = static_cast<int>(gridDim.x);
-            const size_t slot0 = static_cast<size_t>(bh) * (static_cast<size_t>(nseg) * nsplit);
-            const int nsrc = g * nsplit;
-            // a CTA whose share of its segment was empty (fewer chunks than CTAs) stored nothing
-            auto next_stored = [&](int j) {
-              while (j < nsrc) {
-                const int x = j % nsplit;
-                if (p.seg_chunks * (x + 1) / nsplit - p.seg_chunks * x / nsplit > 0) break;
-                ++j;
-              }
-              return j;
-            };
-            uint32_t rc[32];
-            int j = next_stored(0);
-            while (j < nsrc) {
-              const int j2 = next_stored(j + 1);
-              load_block(cb, pr.init_base, (slot0 + j) * st_elems, itrans, rb);
-              if (j2 < nsrc) load_block(cb, pr.init_base, (slot0 + j2) * st_elems, itrans, rc);
-              accumulate(rb);
-              if (j2 < nsrc) accumulate(rc);
-              j = j2 < nsrc ? next_stored(j2 + 1) : nsrc;
-            }
-          }
-          if (pr.bound_out != nullptr && g > 0 && row < p.st_rows) {
-            float* dst = pr.bound_out + (static_cast<size_t>(bh) * (nseg - 1) + (g - 1)) * st_elems;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (cb * 32 + j < p.st_cols)
-                __stcg(dst + static_cast<size_t>(cb * 32 + j) * p.st_rows + row, __uint_as_float(ra[j]));
-          }
-        }
-        ptx::tmem_st32(lane_base + cfg::S_COL + cb * 32, ra);
-        if (row < DK) store_sb(cb, ra);
-      }
-      ptx::tc_wait_st();
-      ptx::fence_proxy_async_smem();
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(sb_ready);
-    }
+    // Everything a converter thread does before the chunk loop (fused form: partial sum, barriers,
+    // scan; then the starting state into TMEM and the operand buffer) lives in a function of its
+    // own, so that its register needs stay out of the allocation of the loops below.
+    PrologueArgs pa;
+    pa.prob_idx = prob_idx;
+    pa.g = g;
+    pa.nseg = nseg;
+    pa.bh = bh;
+    pa.a_iter = a_iter;
+    pa.tmem_base = tmem_base;
+    pa.sb_addr = sb_addr;
+    pa.ost_addr = ost_addr;
+    pa.s_full = s_full;
+    pa.part_done = part_done;
+    pa.grid_done = grid_done;
+    pa.sb_ready = sb_ready;
+    pa.abort_flag = abort_flag;
+    const bool conv_ok = converter_prologue<DK, DV, HALF>(p, pa);
 
     // phase A, if it ran, used the first phase of s_full
     const uint32_t s_off = a_iter > 0 ? 1u : 0u;
@@ -720,24 +922,25 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
           constexpr int MODE = decltype(mode_c)::value;
           constexpr bool kUpper = MODE != 0;
           uint32_t pk[16];
-#pragma unroll
-          for (int jb = 0; jb < 2; ++jb) {
-            const int cb = half * 2 + jb;
-            const bool masked = kUpper ? (cb < quad) : (cb > quad);  // warp-uniform
+          const int cb0 = half * 2, cb1 = half * 2 + 1;
+          const bool masked0 = kUpper ? (cb0 < quad) : (cb0 > quad);  // warp-uniform
+          const bool masked1 = kUpper ? (cb1 < quad) : (cb1 > quad);
+          // both blocks are fetched before either is converted: the two TMEM loads are in flight
+          // together and issuer X gets the fp32 tile back as early as possible
+          if (!masked0 && !masked1) {
+            ptx::tmem_ld32x2(lane_base + cfg::P_COL + cb0 * 32, ra, lane_base + cfg::P_COL + cb1 * 32, rb);
+          } else if (!masked0) {
+            ptx::tmem_ld32(lane_base + cfg::P_COL + cb0 * 32, ra);
+          } else if (!masked1) {
+            ptx::tmem_ld32(lane_base + cfg::P_COL + cb1 * 32, rb);
+          }
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(p_read);
+          auto convert_block = [&](int cb, bool masked, const uint32_t (&r)[32]) {
             if (masked) {
 #pragma unroll
               for (int j = 0; j < 16; ++j) pk[j] = 0u;
-              if (jb == 1) {
-                ptx::tc_fence_before();
-                ptx::mbar_arrive(p_read);
-              }
             } else {
-              ptx::tmem_ld32(lane_base + cfg::P_COL + cb * 32, ra);
-              ptx::tc_wait_ld();
-              if (jb == 1) {  // both blocks are in registers: issuer X may overwrite the fp32 tile
-                ptx::tc_fence_before();
-                ptx::mbar_arrive(p_read);
-              }
               if (cb == quad) {
                 // first kept column (upper modes) resp. last kept column (lower) of this row
                 const int edge = (MODE == 2) ? lane + 1 : lane;
@@ -745,14 +948,13 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
                 for (int j = 0; j < 16; ++j) {
                   const bool k0 = kUpper ? (2 * j >= edge) : (2 * j <= edge);
                   const bool k1 = kUpper ? (2 * j + 1 >= edge) : (2 * j + 1 <= edge);
-                  pk[j] = ptx::pack_bf16x2(k0 ? __uint_as_float(ra[2 * j]) : 0.f,
-                                           k1 ? __uint_as_float(ra[2 * j + 1]) : 0.f);
+                  pk[j] = ptx::pack16x2<HALF>(k0 ? __uint_as_float(r[2 * j]) : 0.f,
+                                              k1 ? __uint_as_float(r[2 * j + 1]) : 0.f);
                 }
               } else {
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
-                  pk[j] =
-                      ptx::pack_bf16x2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1]));
+                  pk[j] = ptx::pack16x2<HALF>(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
               }
               if (MODE == 2) {
 #pragma unroll
@@ -760,7 +962,9 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
               }
             }
             ptx::tmem_st16(lane_base + cfg::PB_COL + (i & 1) * 64 + cb * 16, pk);
-          }
+          };
+          convert_block(cb0, masked0, ra);
+          convert_block(cb1, masked1, rb);
         };
         if (tms && !plain_chunk(i)) {
           p_convert(std::integral_constant<int, 2>{});
@@ -809,42 +1013,46 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
       const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
       const uint32_t swz = static_cast<uint32_t>(row & 7);
       uint32_t ra[32], rb[32];
-      uint32_t pk[DV / 2];
       for (int i = 0; i < n_iter; ++i) {
         int ok = ptx::mbar_wait((i & 1) ? o_full1 : o_full0, (i >> 1) & 1, abort_flag) ? 1 : 0;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         ptx::tc_fence_after();
-#pragma unroll
-        for (int cb = 0; cb < DV / 32; cb += 2) {
-          ptx::tmem_ld32(lane_base + cfg::O_COL + cb * 32, ra);
-          ptx::tmem_ld32(lane_base + cfg::O_COL + (cb + 1) * 32, rb);
-          ptx::tc_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            pk[cb * 16 + j] =
-                ptx::pack_bf16x2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1]));
-            pk[(cb + 1) * 16 + j] =
-                ptx::pack_bf16x2(__uint_as_float(rb[2 * j]), __uint_as_float(rb[2 * j + 1]));
-          }
-        }
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(o_free);
         // Every warp stages and stores its own 32 rows (a 64 x 32 box per column group), so no
         // barrier spans the group and nobody waits for a store except the warp that issued it:
         // before overwriting its rows, lane 0 checks that the previous store has read them.
         if (lane == 0) ptx::bulk_wait_group_read0();
         __syncwarp();
         const uint32_t obuf = ost_addr + row * 128;
+        // One 64-column group at a time: two TMEM loads in flight, rounded and written to the
+        // staging rows straight away (16-byte pieces XOR-swizzled by row % 8), so that only 64
+        // accumulator values are ever held in registers.
 #pragma unroll
         for (int gg = 0; gg < cfg::GV; ++gg) {
+          const uint32_t o_col = cfg::O_COL + (cfg::O_BUFS == 2 ? (i & 1) * DV : 0) + gg * 64;
+          ptx::tmem_ld32x2(lane_base + o_col, ra, lane_base + o_col + 32, rb);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int base = gg * 32 + j * 4;
-            ptx::st_shared_v4(obuf + gg * kGroupBytes + ((static_cast<uint32_t>(j) ^ swz) << 4),
-                              pk[base], pk[base + 1], pk[base + 2], pk[base + 3]);
+          for (int j = 0; j < 4; ++j) {
+            ptx::st_shared_v4(
+                obuf + gg * kGroupBytes + ((static_cast<uint32_t>(j) ^ swz) << 4),
+                ptx::pack16x2<HALF>(__uint_as_float(ra[8 * j + 0]), __uint_as_float(ra[8 * j + 1])),
+                ptx::pack16x2<HALF>(__uint_as_float(ra[8 * j + 2]), __uint_as_float(ra[8 * j + 3])),
+                ptx::pack16x2<HALF>(__uint_as_float(ra[8 * j + 4]), __uint_as_float(ra[8 * j + 5])),
+                ptx::pack16x2<HALF>(__uint_as_float(ra[8 * j + 6]), __uint_as_float(ra[8 * j + 7])));
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            ptx::st_shared_v4(
+                obuf + gg * kGroupBytes + ((static_cast<uint32_t>(j + 4) ^ swz) << 4),
+                ptx::pack16x2<HALF>(__uint_as_float(rb[8 * j + 0]), __uint_as_float(rb[8 * j + 1])),
+                ptx::pack16x2<HALF>(__uint_as_float(rb[8 * j + 2]), __uint_as_float(rb[8 * j + 3])),
+                ptx::pack16x2<HALF>(__uint_as_float(rb[8 * j + 4]), __uint_as_float(rb[8 * j + 5])),
+                ptx::pack16x2<HALF>(__uint_as_float(rb[8 * j + 6]), __uint_as_float(rb[8 * j + 7])));
           }
         }
+        ptx::tc_fence_before();
+        // the accumulator has been read: issuer Y may reuse it
+        ptx::mbar_arrive((cfg::O_BUFS == 2 && (i & 1)) ? o_free1 : o_free0);
         ptx::fence_proxy_async_smem();
         __syncwarp();
         const int tok = mem_chunk(i) * kChunk + quad * 32;

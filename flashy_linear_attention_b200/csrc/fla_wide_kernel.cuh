@@ -284,7 +284,7 @@ fla_wide_kernel(const __grid_constant__ WideParams p) {
     const int row = quad * 32 + lane;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
     const uint32_t swz = static_cast<uint32_t>(row & 7);
-    uint32_t ra[32];
+    uint32_t ra[32], rb[32];
     for (int i = 0; i < n_iter; ++i) {
       int ok = ptx::mbar_wait(p_full, i & 1, abort_flag) ? 1 : 0;
       ok = __all_sync(0xffffffffu, ok);
@@ -295,32 +295,38 @@ fla_wide_kernel(const __grid_constant__ WideParams p) {
       auto p_convert = [&](auto upper_c) {
         constexpr bool kUpper = decltype(upper_c)::value;
         uint32_t pk[16];
-#pragma unroll
-        for (int jb = 0; jb < 2; ++jb) {
-          const int cb = half * 2 + jb;
-          const bool masked = kUpper ? (cb < quad) : (cb > quad);  // warp-uniform
+        const int cb0 = half * 2, cb1 = half * 2 + 1;
+        const bool masked0 = kUpper ? (cb0 < quad) : (cb0 > quad);  // warp-uniform
+        const bool masked1 = kUpper ? (cb1 < quad) : (cb1 > quad);
+        // both blocks are fetched before either is converted (two TMEM loads in flight together)
+        if (!masked0 && !masked1) {
+          ptx::tmem_ld32x2(lane_base + cfg::P_COL + cb0 * 32, ra, lane_base + cfg::P_COL + cb1 * 32, rb);
+        } else if (!masked0) {
+          ptx::tmem_ld32(lane_base + cfg::P_COL + cb0 * 32, ra);
+        } else if (!masked1) {
+          ptx::tmem_ld32(lane_base + cfg::P_COL + cb1 * 32, rb);
+        }
+        auto convert_block = [&](int cb, bool masked, const uint32_t (&r)[32]) {
           if (masked) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) pk[j] = 0u;
-          } else {
-            ptx::tmem_ld32(lane_base + cfg::P_COL + cb * 32, ra);
-            ptx::tc_wait_ld();
-            if (cb == quad) {
+          } else if (cb == quad) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const bool k0 = kUpper ? (2 * j >= lane) : (2 * j <= lane);
-                const bool k1 = kUpper ? (2 * j + 1 >= lane) : (2 * j + 1 <= lane);
-                pk[j] = ptx::pack_bf16x2(k0 ? __uint_as_float(ra[2 * j]) : 0.f,
-                                         k1 ? __uint_as_float(ra[2 * j + 1]) : 0.f);
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j)
-                pk[j] = ptx::pack_bf16x2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1]));
+            for (int j = 0; j < 16; ++j) {
+              const bool k0 = kUpper ? (2 * j >= lane) : (2 * j <= lane);
+              const bool k1 = kUpper ? (2 * j + 1 >= lane) : (2 * j + 1 <= lane);
+              pk[j] = ptx::pack_bf16x2(k0 ? __uint_as_float(r[2 * j]) : 0.f,
+                                       k1 ? __uint_as_float(r[2 * j + 1]) : 0.f);
             }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              pk[j] = ptx::pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
           }
           ptx::tmem_st16(lane_base + cfg::PB_COL + cb * 16, pk);
-        }
+        };
+        convert_block(cb0, masked0, ra);
+        convert_block(cb1, masked1, rb);
       };
       if (upper_flag) {
         p_convert(std::true_type{});
@@ -342,7 +348,6 @@ fla_wide_kernel(const __grid_constant__ WideParams p) {
         for (int t = 0; t < NT; ++t) {
           if (quad * 32 < (((pair_cols(t) + 15) >> 4) << 4)) {  // warp-uniform: rows the MMAs read
             ptx::tmem_ld32(lane_base + cfg::S_COL + t * 64 + half * 32, ra);
-            ptx::tc_wait_ld();
             const uint32_t dst = sb_addr + static_cast<uint32_t>(t * 128 + row) * 128;
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) {
@@ -372,9 +377,8 @@ fla_wide_kernel(const __grid_constant__ WideParams p) {
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tc_fence_after();
-      ptx::tmem_ld32(lane_base + cfg::O_COL, ra);
-      ptx::tmem_ld32(lane_base + cfg::O_COL + 32, rb);
-      ptx::tc_wait_ld();
+      ptx::tmem_ld32x2(lane_base + cfg::O_COL, ra,
+                       lane_base + cfg::O_COL + 32, rb);
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         pk[j] = ptx::pack_bf16x2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1]));

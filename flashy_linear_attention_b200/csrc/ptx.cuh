@@ -5,6 +5,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 
 namespace fla {
@@ -83,20 +84,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
-// Grid-wide barrier for a launch whose CTAs are all resident (cooperative launch). Called by ONE
+// Barrier between CTAs of one launch that are all resident (cooperative launch). Called by ONE
 // thread per CTA, after the CTA's earlier global writes have been fenced. bar[0] counts arrivals,
-// bar[1] is the generation; the last arrival resets the count and bumps the generation, so the two
-// words need no initialisation beyond being zero before their first use. The wait is bounded like
-// every other wait here; a CTA that gives up withdraws its arrival and sets the abort flag.
-__device__ __forceinline__ bool grid_barrier(unsigned* bar, unsigned n_ctas, volatile int* abort_flag) {
+// bar[1] is the generation: the last arrival resets the count and bumps the generation, so the
+// two words need no initialisation beyond being zero before their first use and may serve
+// launches with different CTA counts one after the other. `gen_before` is the generation read at
+// any time before this CTA arrives (it cannot change until it does; reading it early, see
+// barrier_generation(), takes a memory round trip off the barrier). The wait is bounded like every
+// other wait here; a CTA that gives up withdraws its arrival and sets the abort flag.
+__device__ __forceinline__ unsigned barrier_generation(const unsigned* bar) {
   unsigned gen;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(gen) : "l"(bar + 1) : "memory");
-  __threadfence();
-  const unsigned prev = atomicAdd(bar, 1u);
+  return gen;
+}
+__device__ __forceinline__ bool grid_barrier(unsigned* bar, unsigned n_ctas, unsigned gen_before,
+                                             volatile int* abort_flag) {
+  unsigned prev;
+  asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prev) : "l"(bar) : "memory");
   if (prev == n_ctas - 1u) {
-    bar[0] = 0u;
-    __threadfence();
-    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(bar + 1), "r"(gen + 1u) : "memory");
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(bar), "r"(0u) : "memory");
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(bar + 1), "r"(gen_before + 1u) : "memory");
     return true;
   }
   const long long t_start = clock64();
@@ -106,10 +113,7 @@ __device__ __forceinline__ bool grid_barrier(unsigned* bar, unsigned n_ctas, vol
   for (uint32_t spin = 1;; ++spin) {
     unsigned now;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(now) : "l"(bar + 1) : "memory");
-    if (now != gen) {
-      __threadfence();
-      return true;
-    }
+    if (now != gen_before) return true;
     if ((spin & 15u) == 0u && (*abort_flag || clock64() - t_start > limit)) {
       atomicSub(bar, 1u);
       *abort_flag = 1;
@@ -167,9 +171,6 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-__device__ __forceinline__ void tc_wait_ld() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 __device__ __forceinline__ void tc_wait_st() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
@@ -206,11 +207,13 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_
       : "memory");
 }
 
-// Instruction descriptor for kind::f16 with bf16 operands and an fp32 accumulator.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool a_mn_major, bool b_mn_major) {
+// Instruction descriptor for kind::f16 with 16-bit operands (bf16, or fp16 when `half`) and an
+// fp32 accumulator.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool a_mn_major, bool b_mn_major,
+                                                  bool half = false) {
   return (1u << 4)                                // accumulator format: f32
-         | (1u << 7)                              // A format: bf16
-         | (1u << 10)                             // B format: bf16
+         | ((half ? 0u : 1u) << 7)                // A format: 0 = f16, 1 = bf16
+         | ((half ? 0u : 1u) << 10)               // B format
          | ((a_mn_major ? 1u : 0u) << 15)         // A major-ness
          | ((b_mn_major ? 1u : 0u) << 16)         // B major-ness
          | (static_cast<uint32_t>(n >> 3) << 17)  // N / 8
@@ -226,17 +229,31 @@ __device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) 
 }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets lane (base lane + t).
+// tcgen05.ld is asynchronous: its destination registers hold the data only after
+// tcgen05.wait::ld. Load and wait therefore sit in ONE asm statement whose outputs are the
+// destination registers -- with the wait in a statement of its own the compiler is free to schedule
+// arithmetic on those registers between the two (nothing ties a register-only instruction to a
+// volatile asm with a memory clobber), and then it computes on whatever the registers held before.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
+      : "memory");
+}
+// Two such blocks with one wait: both loads are in flight together.
+__device__ __forceinline__ void tmem_ld32x2(uint32_t taddr_a, uint32_t (&a)[32], uint32_t taddr_b,
+                                            uint32_t (&b)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%64];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%65];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]), "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15]), "=r"(a[16]), "=r"(a[17]), "=r"(a[18]), "=r"(a[19]), "=r"(a[20]), "=r"(a[21]), "=r"(a[22]), "=r"(a[23]), "=r"(a[24]), "=r"(a[25]), "=r"(a[26]), "=r"(a[27]), "=r"(a[28]), "=r"(a[29]), "=r"(a[30]), "=r"(a[31]), "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]), "=r"(b[4]), "=r"(b[5]), "=r"(b[6]), "=r"(b[7]), "=r"(b[8]), "=r"(b[9]), "=r"(b[10]), "=r"(b[11]), "=r"(b[12]), "=r"(b[13]), "=r"(b[14]), "=r"(b[15]), "=r"(b[16]), "=r"(b[17]), "=r"(b[18]), "=r"(b[19]), "=r"(b[20]), "=r"(b[21]), "=r"(b[22]), "=r"(b[23]), "=r"(b[24]), "=r"(b[25]), "=r"(b[26]), "=r"(b[27]), "=r"(b[28]), "=r"(b[29]), "=r"(b[30]), "=r"(b[31])
+      : "r"(taddr_a), "r"(taddr_b)
       : "memory");
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -263,6 +280,33 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);  // .x (low 16 bits) = lo, .y = hi
   return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// Two fp32 values rounded to the 16-bit operand type of the kernel instance.
+template <bool HALF>
+__device__ __forceinline__ uint32_t pack16x2(float lo, float hi) {
+  return HALF ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
+}
+// L2-only (cache-global) load; volatile, so that a run of them is issued in program order and stays
+// ahead of the code that consumes the values.
+__device__ __forceinline__ uint32_t ld_global_cg_b32(const float* p) {
+  uint32_t v;
+  asm volatile("ld.global.cg.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Compiler-only fence over 32 registers: everything that produces them (a run of loads) is placed
+// before it and everything that reads them after it, so the loads of a batch are all issued before
+// the first of them is waited for. Emits no instruction.
+__device__ __forceinline__ void keep_together(uint32_t (&r)[32]) {
+  asm volatile(""
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+                 "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]),
+                 "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]),
+                 "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]),
+                 "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]));
 }
 __device__ __forceinline__ void st_shared_b32(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");

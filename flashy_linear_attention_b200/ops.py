@@ -62,7 +62,10 @@ def check_status(device=None) -> None:
         )
 
 
-def _check_inputs(*tensors: torch.Tensor) -> None:
+def _check_inputs(*tensors: torch.Tensor, allow_half: bool = False) -> None:
+    """Device, rank and dtype checks shared by the wrappers. bfloat16 everywhere; the product
+    kernels also take float16 (allow_half) when every tensor of the call is float16 and no head dim
+    exceeds 128."""
     dev = tensors[0].device
     for t in tensors:
         if not t.is_cuda:
@@ -71,11 +74,18 @@ def _check_inputs(*tensors: torch.Tensor) -> None:
             )
         if t.device != dev:
             raise RuntimeError("flashlinear: all tensors must be on the same device")
-        if t.dtype != torch.bfloat16:
-            raise TypeError(
-                f"flashlinear: expected torch.bfloat16 tensors, got {t.dtype} "
-                "(use torch.autocast or cast the inputs)"
-            )
+    if allow_half and all(t.dtype == torch.float16 for t in tensors):
+        if max(t.shape[-1] for t in tensors) > KERNEL_HEAD_DIM:
+            raise TypeError("flashlinear: float16 tensors need head dims <= 128 (wider heads are bfloat16 only)")
+    else:
+        for t in tensors:
+            if t.dtype != torch.bfloat16:
+                raise TypeError(
+                    "flashlinear: expected torch.bfloat16 tensors"
+                    + (" (or torch.float16 throughout)" if allow_half else "")
+                    + f", got {t.dtype} (use torch.autocast or cast the inputs)"
+                )
+    for t in tensors:
         if t.dim() != 4:
             raise ValueError("flashlinear: expected [batch, heads, seq, head_dim] tensors")
 
@@ -157,6 +167,10 @@ def _copy_back(full: torch.Tensor, view: torch.Tensor) -> None:
         full.copy_(view)
 
 
+def _dtype_code(t: torch.Tensor) -> int:
+    return _lib.FLA_DTYPE_F16 if t.dtype == torch.float16 else _lib.FLA_DTYPE_BF16
+
+
 def _desc(t: Optional[torch.Tensor]) -> FlaTensor:
     if t is None:
         return FlaTensor(None, 0, 0, 0)
@@ -212,6 +226,7 @@ def _product_call(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, out: torch.
     args = FlaArgs()
     args.batch, args.heads, args.seqlen, args.dk, args.dv = B, H, N, da, c.shape[-1]
     args.q, args.k, args.v, args.o = _desc(a), _desc(b), _desc(c), _desc(out)
+    args.dtype = _dtype_code(a)
     _call(3, args, a.device, which=1 if anticausal else 0)
 
 
@@ -262,7 +277,8 @@ def causal_dot_product_fwd(
     segment_workspace: Optional[torch.Tensor] = None,
     seg_states: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
-    """out[b,h,i] = sum_{j<=i} (q_i . k_j) v_j, bf16 in / bf16 out, fp32 accumulation.
+    """out[b,h,i] = sum_{j<=i} (q_i . k_j) v_j, bf16 in / bf16 out (or fp16 in / fp16 out for head
+    dims up to 128), fp32 accumulation.
 
     s_init / s_final are optional fp32 [batch*heads, dk, dv] running states (sum of k_j^T v_j
     before / after this call's tokens) for sequence-sharded or resumed calls.
@@ -273,7 +289,7 @@ def causal_dot_product_fwd(
     segment boundaries there, and causal_dot_product_bwd(..., s_last=..., seg_states=...) then runs
     the backward as one launch split at those boundaries (few heads per GPU).
     """
-    _check_inputs(q, k, v)
+    _check_inputs(q, k, v, allow_half=True)
     B, H, N, dk = q.shape
     dv = v.shape[-1]
     if dk > KERNEL_HEAD_DIM or dv > KERNEL_HEAD_DIM:
@@ -285,6 +301,7 @@ def causal_dot_product_fwd(
     a = FlaArgs()
     a.batch, a.heads, a.seqlen, a.dk, a.dv = B, H, N, dk, dv
     a.q, a.k, a.v, a.o = _desc(qv), _desc(kv_), _desc(vv), _desc(ov)
+    a.dtype = _dtype_code(q)
     a.s_init = _fptr(s_init, "s_init", (B * H, dk, dv))
     a.s_final = _fptr(s_final, "s_final", (B * H, dk, dv))
     a.segments = segments
@@ -318,7 +335,7 @@ def causal_dot_product_bwd(
     `s_final`; with it the backward reads q, k, v, dO from HBM only once.
     keep_padded=True: gradients whose head dim is not a multiple of 8 are returned as views of the
     row-padded tensors the kernels wrote, instead of being copied to the contiguous layout."""
-    _check_inputs(grad_output, q, k, v)
+    _check_inputs(grad_output, q, k, v, allow_half=True)
     B, H, N, dk = q.shape
     dv = v.shape[-1]
     wide = KERNEL_HEAD_DIM < dk <= WIDE_HEAD_DIM and dv <= WIDE_NARROW_DIM
@@ -340,6 +357,7 @@ def causal_dot_product_bwd(
     a.batch, a.heads, a.seqlen, a.dk, a.dv = B, H, N, dk, dv
     a.q, a.k, a.v, a.d_o = _desc(qv), _desc(kv_), _desc(vv), _desc(gv)
     a.d_q, a.d_k, a.d_v = _desc(dQv), _desc(dKv), _desc(dVv)
+    a.dtype = _dtype_code(q)
     a.s_init = _fptr(s_init, "s_init", (B * H, dk, dv))
     a.r_init = _fptr(r_init, "r_init", (B * H, dk, dv))
     a.r_final = _fptr(r_final, "r_final", (B * H, dk, dv))
@@ -473,7 +491,9 @@ def taylor_features_bwd(dphi: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
 def backward_uses_final_state(q: torch.Tensor, v: torch.Tensor) -> bool:
     """True when the backward of this shape can take the forward's final state (`s_last`) and sweep
     q, k, v, dO once for all three gradients: it runs unsegmented, or as one launch split at the
-    forward's segment boundaries (then segment_states_buffer() is not None as well)."""
+    forward's segment boundaries (then segment_states_buffer() is not None as well), and the
+    sequence is longer than 2048 tokens (shorter ones keep the two-direction form, which is a
+    little more accurate there)."""
     B, H, N, dk = q.shape
     if dk > KERNEL_HEAD_DIM or v.shape[-1] > KERNEL_HEAD_DIM:
         return False
@@ -481,9 +501,7 @@ def backward_uses_final_state(q: torch.Tensor, v: torch.Tensor) -> bool:
     a.batch, a.heads, a.seqlen, a.dk, a.dv = B, H, N, dk, v.shape[-1]
     a.debug_flags = _debug_flags
     with torch.cuda.device(q.device):
-        lib = _lib.load()
-        return lib.fla_sm100_auto_segments(ctypes.byref(a), 1) <= 1 or \
-            lib.fla_sm100_seg_states_bytes(ctypes.byref(a)) > 0
+        return _lib.load().fla_sm100_bwd_uses_final_state(ctypes.byref(a)) != 0
 
 
 def segment_states_buffer(q: torch.Tensor, v: torch.Tensor, segments: int = 0) -> Optional[torch.Tensor]:
@@ -509,13 +527,14 @@ def chunk_state(b: torch.Tensor, c: torch.Tensor, segments: int = 0, keep_worksp
     these tokens, with (q, dO) the backward state R. Used by sequence-sharded callers.
     keep_workspace=True returns (state, workspace): the scratch then holds the per-segment prefix
     states, which causal_dot_product_fwd(..., segment_workspace=workspace) can reuse."""
-    _check_inputs(b, c)
+    _check_inputs(b, c, allow_half=True)
     B, H, N, db = b.shape
     dc = c.shape[-1]
     bv, cv = _kernel_view(b), _kernel_view(c)
     out = torch.empty(B * H, db, dc, dtype=torch.float32, device=b.device)
     a = FlaArgs()
     a.batch, a.heads, a.seqlen, a.dk, a.dv = B, H, N, db, dc
+    a.dtype = _dtype_code(b)
     a.k, a.v = _desc(bv), _desc(cv)
     a.s_final = out.data_ptr()
     a.segments = segments

