@@ -500,40 +500,56 @@ def main():
                       "out, dQ, dK, dV; max over tensors and ranks", "max_rel": mr, "frob": fr,
                       "tolerance": PARITY_TOL, "ok": bool(mr <= PARITY_TOL and fr <= PARITY_TOL)}
             full_ref = None
-        # The launches of a pass are captured in a CUDA graph and replayed (one graph per pass, so
-        # that the forward / backward split can still be timed with events). The sequence-sharded
-        # path is captured too when it uses the fused peer exchange (its exchange count lives on
-        # the device); the NCCL arm stays eager.
+        # The launches of a step are captured in a CUDA graph and replayed: one graph with the whole
+        # step for the headline time, one graph per pass for the forward / backward split (timed in a
+        # second loop, with an event between the passes). The sequence-sharded path is captured too
+        # when it uses the fused peer exchange (its exchange count lives on the device); the NCCL
+        # arm stays eager.
         launch_mode = "eager"
         run_fwd, run_bwd = step_fwd, step_bwd
+
+        def step_both():
+            step_fwd()
+            step_bwd()
+
+        run_step = step_both
         if (not seq_sharded or peer_ex is not None) and not args.no_graph:
             try:
                 from flashy_linear_attention_b200.graphs import capture_step
-                g_fwd, g_bwd = capture_step(step_fwd), capture_step(step_bwd)
-                run_fwd, run_bwd = g_fwd, g_bwd
-                launch_mode = "one CUDA graph replay per pass"
+                g_fwd, g_bwd, g_step = capture_step(step_fwd), capture_step(step_bwd), capture_step(step_both)
+                run_fwd, run_bwd, run_step = g_fwd, g_bwd, g_step
+                launch_mode = "one CUDA graph replay per step"
                 for _ in range(3):
-                    run_fwd(); run_bwd()
+                    run_fwd(); run_bwd(); run_step()
                 barrier()
                 ops.check_status(device)
             except Exception as exc:  # capture is an optimisation of the host side only
                 launch_mode = f"eager (graph capture failed: {type(exc).__name__})"
-                run_fwd, run_bwd = step_fwd, step_bwd
-        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+                run_fwd, run_bwd, run_step = step_fwd, step_bwd, step_both
+        t0_ev, t1_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         t_region0 = time.time()
+        t0_ev.record(stream)
         for i in range(steps):
+            run_step()
+        t1_ev.record(stream)
+        barrier()
+        clocks = sampler.stop(t_region0, time.time()) if sampler else None
+        ops.check_status(device)
+        total_ms = t0_ev.elapsed_time(t1_ev)
+        # forward / backward split: same kernels, one graph per pass, an event between the passes
+        split_steps = min(steps, 50)
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(split_steps)]
+        for i in range(split_steps):
             ev[i][0].record(stream)
             run_fwd()
             ev[i][1].record(stream)
             run_bwd()
             ev[i][2].record(stream)
         barrier()
-        clocks = sampler.stop(t_region0, time.time()) if sampler else None
         ops.check_status(device)
-        total_ms = ev[0][0].elapsed_time(ev[-1][2])
-        fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / steps
-        bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / steps
+        fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / split_steps
+        bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / split_steps
         total_ms, fwd_ms, bwd_ms = max_over_ranks([total_ms, fwd_ms, bwd_ms])
         res = {
             "ms_per_step": total_ms / steps, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "steps": steps, "warmup": warmup,

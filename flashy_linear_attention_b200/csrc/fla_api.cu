@@ -535,9 +535,16 @@ int auto_segments(int nprob, int bh, int nchunks, int sm_count) {
   return (nchunks + seg_chunks - 1) / seg_chunks;
 }
 
+// Floats one state takes in the scratch of a segmented call: the fused form stores states padded
+// to the kernel's tile (64 x 64 or 128 x 128), whatever the head dims are.
+size_t scratch_state_elems(int rows, int cols) {
+  const int t = pick_template(rows, cols);
+  return t > 0 ? static_cast<size_t>(t) * t : static_cast<size_t>(rows) * cols;
+}
+
 size_t segment_ws_bytes(int nprob, int bh, int nseg, int rows, int cols) {
   if (nseg <= 1) return 0;
-  return static_cast<size_t>(nprob) * bh * nseg * rows * cols * sizeof(float);
+  return static_cast<size_t>(nprob) * bh * nseg * scratch_state_elems(rows, cols) * sizeof(float);
 }
 
 struct SegPlan {
@@ -589,7 +596,7 @@ size_t seg_states_bytes(const FlaArgs* a, int sm_count, SegPlan* fwd_out, SegPla
   if (b.nseg <= 1) return 0;
   if (fwd_out) *fwd_out = f;
   if (bwd_out) *bwd_out = b;
-  return static_cast<size_t>(f.nseg - 1) * bh * a->dk * a->dv * sizeof(float);
+  return static_cast<size_t>(f.nseg - 1) * bh * scratch_state_elems(a->dk, a->dv) * sizeof(float);
 }
 
 template <int D>
@@ -1162,7 +1169,7 @@ int fla_sm100_bwd(const FlaArgs* a) {
       if (a->s_init == nullptr) pq.flags |= fla::kFlagFirstChunkExact;
       pq.ext_init = a->s_last;  // segment 0 of the descending walk: the end of the sequence
       pq.bound_base = static_cast<const float*>(a->seg_states);
-      pq.bound_trans = 0;       // stored as S in the scratch layout = S^T row-major
+      pq.bound_trans = 1;       // the forward stored S^T, which is this product's own state
       pq.bound_stride = f.nseg - 1;
       pq.bound_slot0 = nchunks / f.seg_chunks - 1;
       pq.bound_step = bp.seg_chunks / f.seg_chunks;

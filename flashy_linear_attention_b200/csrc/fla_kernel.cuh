@@ -205,7 +205,53 @@ __device__ __noinline__ bool converter_prologue(const KernelParams& p, const Pro
     }
   };
 
-    bool conv_ok = true;
+  // Scratch of the fused form (partial sums, scanned prefixes, stored boundary states): one state
+  // is DK x DV floats whatever the real head dims are (the rows and columns beyond them hold the
+  // zeros the MMAs produce from zero-filled tiles), in "fragment order": element (r, c) sits at
+  // ((c / 4) * DK + r) * 4 + c % 4. A thread owns a row, so its 32 columns of a block are eight
+  // 16-byte vectors DK * 16 bytes apart, and a warp's vector access covers 512 contiguous bytes.
+  // All strides are compile-time constants: the code that moves a block is 8 (or, for the
+  // transposed read, 32) instructions with immediate offsets. That matters more than the byte
+  // count: this code runs once per CTA, straight from a cold instruction cache.
+  constexpr size_t kFragElems = static_cast<size_t>(DK) * DV;
+  constexpr int kFragVecStride = DK * 16;  // bytes between consecutive 4-column groups of a row
+  auto store_frag = [&](float* state, int cb, const uint32_t (&r)[32]) {
+    float* ptr = state + (static_cast<size_t>(cb) * 8 * DK + row) * 4;
+    ptx::static_for<8>([&](auto i) {
+      constexpr int I = decltype(i)::value;
+      ptx::st_global_cg_v4<I * kFragVecStride>(ptr, r[4 * I], r[4 * I + 1], r[4 * I + 2], r[4 * I + 3]);
+    });
+  };
+  auto load_frag = [&](const float* state, int cb, uint32_t (&r)[32]) {
+    const float* ptr = state + (static_cast<size_t>(cb) * 8 * DK + row) * 4;
+    ptx::static_for<8>([&](auto i) {
+      constexpr int I = decltype(i)::value;
+      ptx::ld_global_cg_v4<I * kFragVecStride>(ptr, r[4 * I], r[4 * I + 1], r[4 * I + 2], r[4 * I + 3]);
+    });
+    ptx::keep_together(r);
+  };
+  // Stores the transpose: element (row, col) of the product goes to position (r = col, c = row).
+  // Stores are not waited for, so the 32 scalar instructions cost issue slots only; the reader
+  // (the dQ product of a later backward call, whose state is the transpose) then loads vectors.
+  auto store_frag_transposed = [&](float* state, int cb, const uint32_t (&r)[32]) {
+    float* ptr = state + (static_cast<size_t>(row >> 2) * DK + cb * 32) * 4 + (row & 3);
+    ptx::static_for<32>([&](auto j) {
+      constexpr int J = decltype(j)::value;
+      ptx::st_global_cg_b32_at<J * 16>(ptr, r[J]);
+    });
+  };
+  // The stored state is the transpose of this product's state: element (row, col) of the product
+  // is stored element (r = col, c = row).
+  auto load_frag_transposed = [&](const float* state, int cb, uint32_t (&r)[32]) {
+    const float* ptr = state + (static_cast<size_t>(row >> 2) * DK + cb * 32) * 4 + (row & 3);
+    ptx::static_for<32>([&](auto j) {
+      constexpr int J = decltype(j)::value;
+      r[J] = ptx::ld_global_cg_b32_at<J * 16>(ptr);
+    });
+    ptx::keep_together(r);
+  };
+
+  bool conv_ok = true;
   unsigned gen0 = 0, gen1 = 0;  // barrier generations, fetched while phase A still runs
   if (fused && warp == 2 && lane == 0) {
     gen0 = ptx::barrier_generation(&g_grid_barriers[((bar_slot * kBarHeads + bh) * 2 + 0) * 2]);
@@ -222,17 +268,12 @@ __device__ __noinline__ bool converter_prologue(const KernelParams& p, const Pro
         ptx::tc_fence_after();
         const size_t slot = static_cast<size_t>(bh) * (static_cast<size_t>(nseg) * gridDim.x) +
                             static_cast<size_t>(g) * gridDim.x + blockIdx.x;
-        float* dst = part_out + slot * st_elems;
+        float* dst = part_out + slot * kFragElems;
 #pragma unroll 1
         for (int jb = 0; jb < SBLK; ++jb) {
           const int cb = half * SBLK + jb;
           ptx::tmem_ld32(lane_base + cfg::S_COL + cb * 32, ra);
-          if (row < st_rows) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (cb * 32 + j < st_cols)
-                __stcg(dst + static_cast<size_t>(cb * 32 + j) * st_rows + row, __uint_as_float(ra[j]));
-          }
+          if (row < DK) store_frag(dst, cb, ra);
         }
         ptx::tc_fence_before();
       }
@@ -265,53 +306,45 @@ __device__ __noinline__ bool converter_prologue(const KernelParams& p, const Pro
     };
     head_barrier(0, gen0);
     if (conv_ok && nseg > 1) {
-      // ---------------- scan: partial sums -> exclusive prefixes per segment, in place. This CTA
-      // owns one slice of the state's elements for ALL segments of its head. Slots are walked in
-      // order (slot j = segment j / nsplit, share j % nsplit); after the last share of segment
-      // s the running sum is the prefix of segment s + 1 and overwrites slot (s + 1) * nsplit.
-      // kScanSlots slots of kScanElems elements are loaded at a time, all loads before the first
-      // use; a prefix whose slot is the first one of the NEXT batch is written only after that
-      // batch has been loaded (its partial is still needed).
-      constexpr int kScanSlots = 8, kScanElems = 4;
+      // ---------------- scan: partial sums -> exclusive prefixes per segment, in place. The
+      // head's CTAs share the state's 16-byte vectors (units of 256, one vector per thread); a
+      // thread walks ALL slots of its vector in order (slot j = segment j / nsplit, share
+      // j % nsplit): after the last share of segment s the running sum is the prefix of segment
+      // s + 1 and overwrites slot (s + 1) * nsplit. kScanSlots slots are loaded at a time, all
+      // loads before the first use; a prefix whose slot is the first one of the NEXT batch is
+      // written only after that batch has been loaded (its partial is still needed).
+      constexpr int kScanSlots = 8;
+      constexpr int kUnits = static_cast<int>(kFragElems / 4 / 256);
       const int nsplit = static_cast<int>(gridDim.x);
-      const int elems = static_cast<int>(st_elems);
-      const int slice = (elems + static_cast<int>(head_ctas) - 1) / static_cast<int>(head_ctas);
-      const int lo = (g * nsplit + static_cast<int>(blockIdx.x)) * slice;
-      const int hi = min(elems, lo + slice);
       const int tid = (warp - 2) * 32 + lane;
-      float* hb = part_out + static_cast<size_t>(bh) * (static_cast<size_t>(nseg) * nsplit) * st_elems;
-      const int nslots = (nseg - 1) * nsplit;  // slots that can hold a partial
+      float* hb = part_out + static_cast<size_t>(bh) * (static_cast<size_t>(nseg) * nsplit) * kFragElems;
+      const int nslots = (nseg - 1) * nsplit;    // slots that can hold a partial
+      const int last_slot = nseg * nsplit - 1;   // last slot of this head's scratch
       // bit x: share x of a segment is not empty (a CTA with an empty share stored nothing)
       unsigned stored_mask = 0;
       for (int x = 0; x < nsplit; ++x)
         if (seg_chunks * (x + 1) / nsplit - seg_chunks * x / nsplit > 0) stored_mask |= 1u << x;
 #pragma unroll 1
-      for (int e0 = lo + tid; e0 < hi; e0 += 256 * kScanElems) {
-        float run[kScanElems], pending[kScanElems];
-#pragma unroll
-        for (int u = 0; u < kScanElems; ++u) run[u] = 0.f;
+      for (int unit = g * nsplit + static_cast<int>(blockIdx.x); unit < kUnits;
+           unit += static_cast<int>(head_ctas)) {
+        float* vec = hb + (static_cast<size_t>(unit) * 256 + tid) * 4;
+        float run[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t pending[4] = {0u, 0u, 0u, 0u};
         bool have_pending = false;
         int x0 = 0;  // share index of slot j0
 #pragma unroll 1
         for (int j0 = 0; j0 < nslots; j0 += kScanSlots) {
-          uint32_t val[kScanElems * kScanSlots];
-          static_assert(kScanElems * kScanSlots == 32, "one keep_together() per batch");
+          uint32_t val[4 * kScanSlots];
+          static_assert(4 * kScanSlots == 32, "one keep_together() per batch");
 #pragma unroll
-          for (int u = 0; u < kScanElems; ++u) {
-            const int e = e0 + 256 * u;
-#pragma unroll
-            for (int jj = 0; jj < kScanSlots; ++jj) {
-              const int j = j0 + jj;
-              const bool want = e < hi && j < nslots;
-              val[u * kScanSlots + jj] =
-                  ptx::ld_global_cg_b32(hb + (want ? static_cast<size_t>(j) * st_elems + e : 0));
-            }
+          for (int jj = 0; jj < kScanSlots; ++jj) {
+            const float* src = vec + static_cast<size_t>(min(j0 + jj, last_slot)) * kFragElems;
+            ptx::ld_global_cg_v4<0>(src, val[4 * jj], val[4 * jj + 1], val[4 * jj + 2], val[4 * jj + 3]);
           }
           ptx::keep_together(val);  // all loads of the batch before any store
           if (have_pending) {       // prefix held back by the batch before: its slot is j0
-#pragma unroll
-            for (int u = 0; u < kScanElems; ++u)
-              if (e0 + 256 * u < hi) __stcg(hb + static_cast<size_t>(j0) * st_elems + e0 + 256 * u, pending[u]);
+            ptx::st_global_cg_v4<0>(vec + static_cast<size_t>(j0) * kFragElems, pending[0], pending[1],
+                                    pending[2], pending[3]);
             have_pending = false;
           }
           int x = x0;
@@ -319,20 +352,23 @@ __device__ __noinline__ bool converter_prologue(const KernelParams& p, const Pro
           for (int jj = 0; jj < kScanSlots; ++jj) {
             const int j = j0 + jj;
             if (j < nslots) {
-              const bool add = (stored_mask >> x) & 1u;
               const bool seg_end = x + 1 == nsplit;
-              // the prefix goes to slot j + 1; if that is the first slot of the next batch, later
-              const bool defer = jj == kScanSlots - 1 && j + 1 < nslots;
+              if ((stored_mask >> x) & 1u) {
 #pragma unroll
-              for (int u = 0; u < kScanElems; ++u) {
-                if (add) run[u] += __uint_as_float(val[u * kScanSlots + jj]);
-                if (seg_end) {
-                  if (defer) pending[u] = run[u];
-                  else if (e0 + 256 * u < hi)
-                    __stcg(hb + static_cast<size_t>(j + 1) * st_elems + e0 + 256 * u, run[u]);
+                for (int u = 0; u < 4; ++u) run[u] += __uint_as_float(val[4 * jj + u]);
+              }
+              if (seg_end) {
+                // the prefix goes to slot j + 1; if that is the first slot of the next batch, later
+                if (jj == kScanSlots - 1 && j + 1 < nslots) {
+#pragma unroll
+                  for (int u = 0; u < 4; ++u) pending[u] = __float_as_uint(run[u]);
+                  have_pending = true;
+                } else {
+                  ptx::st_global_cg_v4<0>(vec + static_cast<size_t>(j + 1) * kFragElems,
+                                          __float_as_uint(run[0]), __float_as_uint(run[1]),
+                                          __float_as_uint(run[2]), __float_as_uint(run[3]));
                 }
               }
-              if (seg_end && defer) have_pending = true;
               x = seg_end ? 0 : x + 1;
             }
           }
@@ -355,7 +391,39 @@ __device__ __noinline__ bool converter_prologue(const KernelParams& p, const Pro
     // them) and the step is pure latency otherwise. Row-major arrays are fetched along rows by
     // the lanes (whole 128-byte segments per warp instruction) and settle() then exchanges them
     // through the output staging buffer, which is idle before chunk 0.
+    const bool full_tile = st_rows == DK && st_cols == DV;  // no element of a block is padding
     auto fetch = [&](int cb, const float* base, bool trans, uint32_t (&r)[32]) {
+      if (full_tile) {
+        // same access patterns as below with every offset an immediate and no bounds tests: a
+        // quarter of the instructions, which is what this once-per-CTA code costs in
+        if (trans) {
+          const float* ptr = base + static_cast<size_t>(cb) * 32 * DK + row;
+          ptx::static_for<32>([&](auto j) {
+            constexpr int J = decltype(j)::value;
+            r[J] = ptx::ld_global_cg_b32_at<J * DK * 4>(ptr);
+          });
+        } else if (kStagedStateIO) {
+          const float* ptr = base + static_cast<size_t>(quad) * 32 * DV + cb * 32 + lane;
+          ptx::static_for<32>([&](auto j) {
+            constexpr int J = decltype(j)::value;
+            r[J] = ptx::ld_global_cg_b32_at<J * DV * 4>(ptr);
+          });
+        } else {
+          const float* ptr = base + static_cast<size_t>(row < DK ? row : 0) * DV + cb * 32;
+          ptx::static_for<8>([&](auto j) {
+            constexpr int J = decltype(j)::value;
+            ptx::ld_global_cg_v4<J * 16>(ptr, r[4 * J], r[4 * J + 1], r[4 * J + 2], r[4 * J + 3]);
+          });
+        }
+        ptx::keep_together(r);
+        if (!kStagedStateIO || trans) {
+          if (row >= DK) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0u;
+          }
+        }
+        return;
+      }
       if (kStagedStateIO && !trans) {
         const int col = cb * 32 + lane;
 #pragma unroll
@@ -394,62 +462,66 @@ __device__ __noinline__ bool converter_prologue(const KernelParams& p, const Pro
         __syncwarp();
       }
     };
-    const float* add = nullptr;   // caller's state
-    const float* src = nullptr;   // first of the nsrc arrays
-    bool add_trans = pr.add_trans != 0, src_trans = false;
-    size_t stride = 0;
-    int nsrc = 0;
+    const bool add_trans = pr.add_trans != 0;
     const size_t head_index = static_cast<size_t>(bh) * st_elems;
     if (!fused) {
-      src = pr.s_init + st_index;
-      src_trans = st_trans;
-      nsrc = 1;
-      if (pr.s_add != nullptr) add = pr.s_add + head_index;
+      // one array in the layout the state pass / the caller wrote, plus the caller's state
+      const float* src = pr.s_init + st_index;
+      const float* add = pr.s_add != nullptr ? pr.s_add + head_index : nullptr;
+#pragma unroll 1
+      for (int jb = 0; jb < SBLK; ++jb) {
+        const int cb = half * SBLK + jb;
+        fetch(cb, src, st_trans, ra);
+        settle(st_trans, ra);
+        if (add != nullptr) {
+          fetch(cb, add, add_trans, rb);
+          settle(add_trans, rb);
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            ra[c] = __float_as_uint(__uint_as_float(ra[c]) + __uint_as_float(rb[c]));
+        }
+        ptx::tmem_st32(lane_base + cfg::S_COL + cb * 32, ra);
+        if (row < DK) store_sb(cb, ra);
+      }
     } else {
-      // caller's state: every segment for kInitParts, the first one only for kInitBound
+      static_assert(DK == DV, "the transposed read of a stored state assumes square scratch states");
+      // Fused form. Segment g >= 1 starts from ONE scratch state: the scanned prefix of its
+      // segment (slot g * nsplit of the head) or a boundary state an earlier call stored; the
+      // caller's state is added for every segment (partial sums) or is all segment 0 has (boundary
+      // states). `own`: the scratch state has this product's orientation.
       const bool bound = pr.init_kind == kInitBound;
-      if (pr.s_add != nullptr && (!bound || g == 0)) add = pr.s_add + head_index;
-      src_trans = pr.init_trans != 0;
-      stride = st_elems;
-      if (bound) {
-        const size_t slot = static_cast<size_t>(bh) * pr.init_stride + (pr.bound_slot0 - g * pr.bound_step);
-        src = pr.init_base + slot * st_elems;
-        nsrc = g > 0 ? 1 : 0;
-      } else {
-        // the scanned prefix of this segment (slot g * nsplit of the head); segment 0 has none
-        const int slots = static_cast<int>(gridDim.x);
-        src = pr.init_base + (static_cast<size_t>(bh) * (static_cast<size_t>(nseg) * slots) +
-                              static_cast<size_t>(g) * slots) * st_elems;
-        nsrc = g > 0 ? 1 : 0;
+      const float* add = (pr.s_add != nullptr && (!bound || g == 0)) ? pr.s_add + head_index : nullptr;
+      const bool own = pr.init_trans != 0;
+      const float* src = nullptr;
+      if (g > 0) {
+        const size_t slot = bound ? static_cast<size_t>(bh) * pr.init_stride + (pr.bound_slot0 - g * pr.bound_step)
+                                  : (static_cast<size_t>(bh) * nseg + g) * gridDim.x;
+        src = pr.init_base + slot * kFragElems;
       }
-    }
+      float* keep = (bound_out != nullptr && g > 0)
+                        ? bound_out + (static_cast<size_t>(bh) * (nseg - 1) + (g - 1)) * kFragElems
+                        : nullptr;
 #pragma unroll 1
-    for (int jb = 0; jb < SBLK; ++jb) {
-      const int cb = half * SBLK + jb;
-      if (add != nullptr) {
-        fetch(cb, add, add_trans, ra);
-        settle(add_trans, ra);
-      } else {
+      for (int jb = 0; jb < SBLK; ++jb) {
+        const int cb = half * SBLK + jb;
+        if (src != nullptr && row < DK) {
+          if (own) load_frag(src, cb, ra);
+          else load_frag_transposed(src, cb, ra);
+        } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) ra[j] = 0u;
-      }
-#pragma unroll 1
-      for (int j = 0; j < nsrc; ++j) {
-        fetch(cb, src + j * stride, src_trans, rb);
-        settle(src_trans, rb);
+          for (int j = 0; j < 32; ++j) ra[j] = 0u;
+        }
+        if (add != nullptr) {
+          fetch(cb, add, add_trans, rb);
+          settle(add_trans, rb);
 #pragma unroll
-        for (int c = 0; c < 32; ++c)
-          ra[c] = __float_as_uint(__uint_as_float(ra[c]) + __uint_as_float(rb[c]));
+          for (int c = 0; c < 32; ++c)
+            ra[c] = __float_as_uint(__uint_as_float(ra[c]) + __uint_as_float(rb[c]));
+        }
+        if (keep != nullptr && row < DK) store_frag_transposed(keep, cb, ra);
+        ptx::tmem_st32(lane_base + cfg::S_COL + cb * 32, ra);
+        if (row < DK) store_sb(cb, ra);
       }
-      if (fused && bound_out != nullptr && g > 0 && row < st_rows) {
-        float* dst = bound_out + (static_cast<size_t>(bh) * (nseg - 1) + (g - 1)) * st_elems;
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (cb * 32 + j < st_cols)
-            __stcg(dst + static_cast<size_t>(cb * 32 + j) * st_rows + row, __uint_as_float(ra[j]));
-      }
-      ptx::tmem_st32(lane_base + cfg::S_COL + cb * 32, ra);
-      if (row < DK) store_sb(cb, ra);
     }
     ptx::tc_wait_st();
     ptx::fence_proxy_async_smem();

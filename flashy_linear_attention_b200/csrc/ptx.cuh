@@ -8,6 +8,8 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include <utility>
+
 namespace fla {
 namespace ptx {
 
@@ -102,8 +104,10 @@ __device__ __forceinline__ bool grid_barrier(unsigned* bar, unsigned n_ctas, uns
   unsigned prev;
   asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prev) : "l"(bar) : "memory");
   if (prev == n_ctas - 1u) {
-    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(bar), "r"(0u) : "memory");
+    // Release first, reset after: nobody arrives at these words again before the launch ends, and
+    // a release that had to wait for the reset to land would cost the waiters a memory round trip.
     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(bar + 1), "r"(gen_before + 1u) : "memory");
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(bar), "r"(0u) : "memory");
     return true;
   }
   const long long t_start = clock64();
@@ -111,9 +115,12 @@ __device__ __forceinline__ bool grid_barrier(unsigned* bar, unsigned n_ctas, uns
   const long long limit = lim_k ? (static_cast<long long>(lim_k) << 10) : kWaitLimitCycles;
 #pragma unroll 1
   for (uint32_t spin = 1;; ++spin) {
-    unsigned now;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(now) : "l"(bar + 1) : "memory");
-    if (now != gen_before) return true;
+    unsigned now;  // relaxed polls, one acquire fence once the generation has moved
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(now) : "l"(bar + 1) : "memory");
+    if (now != gen_before) {
+      asm volatile("fence.acq_rel.gpu;" ::: "memory");
+      return true;
+    }
     if ((spin & 15u) == 0u && (*abort_flag || clock64() - t_start > limit)) {
       atomicSub(bar, 1u);
       *abort_flag = 1;
@@ -296,6 +303,43 @@ __device__ __forceinline__ uint32_t ld_global_cg_b32(const float* p) {
   uint32_t v;
   asm volatile("ld.global.cg.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+// The same for 16 bytes at a compile-time byte offset from `p` (the offset becomes the immediate
+// of the instruction, so a run of these from one base pointer costs one instruction each).
+template <int OFF>
+__device__ __forceinline__ void ld_global_cg_v4(const float* p, uint32_t& a, uint32_t& b, uint32_t& c,
+                                                uint32_t& d) {
+  asm volatile("ld.global.cg.v4.b32 {%0, %1, %2, %3}, [%4 + %5];"
+               : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
+               : "l"(p), "n"(OFF)
+               : "memory");
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t ld_global_cg_b32_at(const float* p) {
+  uint32_t v;
+  asm volatile("ld.global.cg.b32 %0, [%1 + %2];" : "=r"(v) : "l"(p), "n"(OFF) : "memory");
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ void st_global_cg_v4(float* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.global.cg.v4.b32 [%0 + %1], {%2, %3, %4, %5};"
+               :
+               : "l"(p), "n"(OFF), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+template <int OFF>
+__device__ __forceinline__ void st_global_cg_b32_at(float* p, uint32_t v) {
+  asm volatile("st.global.cg.b32 [%0 + %1], %2;" ::"l"(p), "n"(OFF), "r"(v) : "memory");
+}
+// f(std::integral_constant<int, 0>{}) ... f(std::integral_constant<int, N - 1>{}): a loop whose
+// index is a constant expression in the body (template arguments, asm immediates).
+template <class F, int... I>
+__device__ __forceinline__ void static_for_impl(F&& f, std::integer_sequence<int, I...>) {
+  (f(std::integral_constant<int, I>{}), ...);
+}
+template <int N, class F>
+__device__ __forceinline__ void static_for(F&& f) {
+  static_for_impl(f, std::make_integer_sequence<int, N>{});
 }
 // Compiler-only fence over 32 registers: everything that produces them (a run of loads) is placed
 // before it and everything that reads them after it, so the loads of a batch are all issued before
