@@ -86,15 +86,14 @@ struct KernelParams {
   int debug_withhold;  // test hook: the producer skips the load of its first tile, so that the
                        // consumers' bounded wait runs out and the status path is exercised
   // ---- fused segments: ONE launch does what mode 1 + the scan kernel + mode 0 do in three.
-  // Every CTA first sums b^T c over its share of the chunks of its segment (phase A; operands and
-  // walking direction of problem `pre_prob`; the `gridDim.x` CTAs of a (segment, head) split the
-  // segment's chunks between them) and stores the sum as partial (segment * gridDim.x + blockIdx.x)
-  // of its head in part_out. The CTAs of a head then meet at a barrier (the launch must be
-  // cooperative: every CTA resident), turn the partials into per-segment prefixes together (each
-  // CTA scans a slice of the state's elements over all segments, in place: the prefix of segment
-  // s lands in slot s * gridDim.x), meet again, and each CTA takes the prefix of its segment as
-  // its starting state and runs the attention loop. The last segment's own sum is never needed
-  // and is skipped.
+  // Phase A: the sums of b^T c over segments 0 .. segments - 2 are needed (operands and walking
+  // direction of problem `pre_prob`); all gridDim.x * gridDim.y CTAs of a head share that work,
+  // CTA number c (= segment * gridDim.x + blockIdx.x) summing share c % shares of segment
+  // c / shares, and store their sums as slot c of the head in part_out. The CTAs of a head then meet
+  // at a barrier (the launch must be cooperative: every CTA resident), turn the partials into
+  // per-segment prefixes together (each CTA scans some of the state's elements over all slots, in
+  // place: the prefix of segment s lands in slot s * shares - 1), meet again, and each CTA takes
+  // the prefix of its segment as its starting state and runs the attention loop.
   int fused;
   int pre_prob;
   float* part_out;
@@ -267,7 +266,7 @@ __device__ __noinline__ bool converter_prologue(const KernelParams& p, const Pro
       if (ok) {
         ptx::tc_fence_after();
         const size_t slot = static_cast<size_t>(bh) * (static_cast<size_t>(nseg) * gridDim.x) +
-                            static_cast<size_t>(g) * gridDim.x + blockIdx.x;
+                            static_cast<size_t>(g) * gridDim.x + blockIdx.x;  // CTA number within the head
         float* dst = part_out + slot * kFragElems;
 #pragma unroll 1
         for (int jb = 0; jb < SBLK; ++jb) {
@@ -308,29 +307,27 @@ __device__ __noinline__ bool converter_prologue(const KernelParams& p, const Pro
     if (conv_ok && nseg > 1) {
       // ---------------- scan: partial sums -> exclusive prefixes per segment, in place. The
       // head's CTAs share the state's 16-byte vectors (units of 256, one vector per thread); a
-      // thread walks ALL slots of its vector in order (slot j = segment j / nsplit, share
-      // j % nsplit): after the last share of segment s the running sum is the prefix of segment
-      // s + 1 and overwrites slot (s + 1) * nsplit. kScanSlots slots are loaded at a time, all
-      // loads before the first use; a prefix whose slot is the first one of the NEXT batch is
-      // written only after that batch has been loaded (its partial is still needed).
+      // thread walks ALL slots of its vector in order (slot j = share j % shares of segment
+      // j / shares): after the last share of segment s the running sum is the prefix of segment
+      // s + 1 and overwrites that last share's slot, (s + 1) * shares - 1, whose partial has just
+      // been consumed. kScanSlots slots are loaded at a time, all loads before the first use.
       constexpr int kScanSlots = 8;
       constexpr int kUnits = static_cast<int>(kFragElems / 4 / 256);
       const int nsplit = static_cast<int>(gridDim.x);
+      const int shares = static_cast<int>(head_ctas) / (nseg - 1);
       const int tid = (warp - 2) * 32 + lane;
-      float* hb = part_out + static_cast<size_t>(bh) * (static_cast<size_t>(nseg) * nsplit) * kFragElems;
-      const int nslots = (nseg - 1) * nsplit;    // slots that can hold a partial
-      const int last_slot = nseg * nsplit - 1;   // last slot of this head's scratch
+      float* hb = part_out + static_cast<size_t>(bh) * head_ctas * kFragElems;
+      const int nslots = (nseg - 1) * shares;                // slots that can hold a partial
+      const int last_slot = static_cast<int>(head_ctas) - 1;  // last slot of this head's scratch
       // bit x: share x of a segment is not empty (a CTA with an empty share stored nothing)
       unsigned stored_mask = 0;
-      for (int x = 0; x < nsplit; ++x)
-        if (seg_chunks * (x + 1) / nsplit - seg_chunks * x / nsplit > 0) stored_mask |= 1u << x;
+      for (int x = 0; x < shares; ++x)
+        if (seg_chunks * (x + 1) / shares - seg_chunks * x / shares > 0) stored_mask |= 1u << x;
 #pragma unroll 1
       for (int unit = g * nsplit + static_cast<int>(blockIdx.x); unit < kUnits;
            unit += static_cast<int>(head_ctas)) {
         float* vec = hb + (static_cast<size_t>(unit) * 256 + tid) * 4;
         float run[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t pending[4] = {0u, 0u, 0u, 0u};
-        bool have_pending = false;
         int x0 = 0;  // share index of slot j0
 #pragma unroll 1
         for (int j0 = 0; j0 < nslots; j0 += kScanSlots) {
@@ -342,34 +339,23 @@ __device__ __noinline__ bool converter_prologue(const KernelParams& p, const Pro
             ptx::ld_global_cg_v4<0>(src, val[4 * jj], val[4 * jj + 1], val[4 * jj + 2], val[4 * jj + 3]);
           }
           ptx::keep_together(val);  // all loads of the batch before any store
-          if (have_pending) {       // prefix held back by the batch before: its slot is j0
-            ptx::st_global_cg_v4<0>(vec + static_cast<size_t>(j0) * kFragElems, pending[0], pending[1],
-                                    pending[2], pending[3]);
-            have_pending = false;
-          }
           int x = x0;
 #pragma unroll
           for (int jj = 0; jj < kScanSlots; ++jj) {
             const int j = j0 + jj;
             if (j < nslots) {
-              const bool seg_end = x + 1 == nsplit;
               if ((stored_mask >> x) & 1u) {
 #pragma unroll
                 for (int u = 0; u < 4; ++u) run[u] += __uint_as_float(val[4 * jj + u]);
               }
-              if (seg_end) {
-                // the prefix goes to slot j + 1; if that is the first slot of the next batch, later
-                if (jj == kScanSlots - 1 && j + 1 < nslots) {
-#pragma unroll
-                  for (int u = 0; u < 4; ++u) pending[u] = __float_as_uint(run[u]);
-                  have_pending = true;
-                } else {
-                  ptx::st_global_cg_v4<0>(vec + static_cast<size_t>(j + 1) * kFragElems,
-                                          __float_as_uint(run[0]), __float_as_uint(run[1]),
-                                          __float_as_uint(run[2]), __float_as_uint(run[3]));
-                }
+              if (x + 1 == shares) {
+                ptx::st_global_cg_v4<0>(vec + static_cast<size_t>(j) * kFragElems, __float_as_uint(run[0]),
+                                        __float_as_uint(run[1]), __float_as_uint(run[2]),
+                                        __float_as_uint(run[3]));
+                x = 0;
+              } else {
+                ++x;
               }
-              x = seg_end ? 0 : x + 1;
             }
           }
           x0 = x;
@@ -494,8 +480,10 @@ __device__ __noinline__ bool converter_prologue(const KernelParams& p, const Pro
       const bool own = pr.init_trans != 0;
       const float* src = nullptr;
       if (g > 0) {
+        // the scanned prefix of segment g sits in the last share slot of segment g - 1
+        const size_t head_ctas = static_cast<size_t>(nseg) * gridDim.x;
         const size_t slot = bound ? static_cast<size_t>(bh) * pr.init_stride + (pr.bound_slot0 - g * pr.bound_step)
-                                  : (static_cast<size_t>(bh) * nseg + g) * gridDim.x;
+                                  : static_cast<size_t>(bh) * head_ctas + g * (head_ctas / (nseg - 1)) - 1;
         src = pr.init_base + slot * kFragElems;
       }
       float* keep = (bound_out != nullptr && g > 0)
@@ -595,11 +583,20 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
   // problem whose state is being summed. The last segment's sum is not needed by anyone.
   const Problem& pre = p.prob[fused ? p.pre_prob : prob_idx];
   const bool pre_desc = (pre.flags & kFlagDescending) != 0;
-  int a_lo = 0, a_iter = 0;
-  if (fused && g < nseg - 1) {
-    const int nsplit = static_cast<int>(gridDim.x);
-    a_lo = n_iter * static_cast<int>(blockIdx.x) / nsplit;
-    a_iter = n_iter * (static_cast<int>(blockIdx.x) + 1) / nsplit - a_lo;
+  int a_lo = 0, a_iter = 0, a_chunk0 = 0;
+  if (fused && nseg > 1) {
+    // The nseg - 1 segments whose sums are needed are shared by ALL CTAs of the head, `shares` per
+    // segment (the CTA that later walks the last segment sums too): CTA number c of the head takes
+    // share c % shares of segment c / shares. Partial c goes to slot c of the head's scratch.
+    const int head_ctas = nseg * static_cast<int>(gridDim.x);
+    const int c = g * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x);
+    const int shares = head_ctas / (nseg - 1);
+    if (c < shares * (nseg - 1)) {
+      const int sa = c / shares, xa = c - sa * shares;
+      a_chunk0 = sa * p.seg_chunks;
+      a_lo = p.seg_chunks * xa / shares;
+      a_iter = p.seg_chunks * (xa + 1) / shares - a_lo;
+    }
   }
   const int t0 = 2 * a_iter;  // the tiles of phase A come first in the ring numbering
   const size_t st_elems = static_cast<size_t>(p.st_rows) * p.st_cols;
@@ -670,7 +667,7 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
   // chunk i is computed without the state (see kFlagFirstChunkExact)
   auto plain_chunk = [&](int i) { return exact0 && mem_chunk(i) == 0; };
   auto pre_mem_chunk = [&](int i) {
-    const int c = chunk0 + a_lo + i;
+    const int c = a_chunk0 + a_lo + i;
     return pre_desc ? (p.nchunks - 1 - c) : c;
   };
   auto slot_addr = [&](int t) {
