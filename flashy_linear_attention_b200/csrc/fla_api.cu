@@ -565,7 +565,19 @@ SegPlan make_plan(int want, int nchunks) {
 SegPlan forward_plan(const FlaArgs* a, int sm_count) {
   const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
   const int want = a->segments > 0 ? a->segments : auto_segments(1, a->batch * a->heads, nchunks, sm_count);
-  return make_plan(want, nchunks);
+  SegPlan p = make_plan(want, nchunks);
+  if (a->segments <= 0 && p.nseg > 1 && nchunks % p.seg_chunks != 0) {
+    // An automatic split prefers equal segments (up to a quarter longer than the even share): the
+    // backward can then be cut at a subset of the forward's boundaries and start from its states.
+    for (int d = p.seg_chunks + 1; d <= p.seg_chunks + p.seg_chunks / 4; ++d) {
+      if (nchunks % d == 0) {
+        p.seg_chunks = d;
+        p.nseg = nchunks / d;
+        break;
+      }
+    }
+  }
+  return p;
 }
 
 // Segments of a backward call (three products per head) whose boundaries are boundaries of the
@@ -1096,10 +1108,15 @@ int fla_sm100_fwd(const FlaArgs* a) {
     return run_wide_a(p, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->status,
                       static_cast<cudaStream_t>(a->stream));
   if (a->seg_states != nullptr && a->segment_states_ready == 0) {
-    const size_t need = seg_states_bytes(a, dev->sm_count, nullptr, nullptr);
+    SegPlan f, b;
+    const size_t need = seg_states_bytes(a, dev->sm_count, &f, &b);
     if (need > 0) {
       if (a->seg_states_bytes < need) return FLA_ERR_WORKSPACE;
       p.bound_out = static_cast<float*>(a->seg_states);
+      // the segments the backward's plan was made for
+      return run_products(&p, 1, a->batch, a->heads, a->seqlen, a->dk, a->dv, f.nseg, a->workspace,
+                          a->workspace_bytes, a->status, static_cast<cudaStream_t>(a->stream), *dev,
+                          false, f.seg_chunks);
     }
   }
   return run_products(&p, 1, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->segments,
