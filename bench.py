@@ -48,9 +48,10 @@ UNIT = "Mtokens/s"
 PARITY_TOL = 2e-2
 
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the forward and the backward launch
-# of one cfg3 step, from a separate ncu capture of this workload: a constant, not a measurement of
-# the run that prints it. Other workloads report null.
-NCU_TRAFFIC_BYTES_PER_STEP = {"cfg3": 2.909e9}
+# of one cfg3 step: a constant, not a measurement of the run that prints it. It comes from an ncu
+# capture of the same grids at half the sequence length (518.1 + 952.6 MB), doubled: the traffic of
+# these launches grows in proportion to N. Other workloads report null.
+NCU_TRAFFIC_BYTES_PER_STEP = {"cfg3": 2.941e9}
 
 
 def measured_peaks():
@@ -500,17 +501,22 @@ def main():
                       "out, dQ, dK, dV; max over tensors and ranks", "max_rel": mr, "frob": fr,
                       "tolerance": PARITY_TOL, "ok": bool(mr <= PARITY_TOL and fr <= PARITY_TOL)}
             full_ref = None
-        # The launches of a step are captured in a CUDA graph and replayed: one graph with the whole
-        # step for the headline time, one graph per pass for the forward / backward split (timed in a
-        # second loop, with an event between the passes). The sequence-sharded path is captured too
+        # The launches are captured in CUDA graphs and replayed: for the headline time one graph that
+        # holds `per_graph` whole steps back to back (what a training step with several attention
+        # layers looks like to the GPU; a graph launch costs ~5 us, which at 16 heads per GPU is 4 %
+        # of a step), one graph per pass for the forward / backward split (timed in a second loop,
+        # with an event between the passes). The sequence-sharded path is captured too
         # when it uses the fused peer exchange (its exchange count lives on the device); the NCCL
         # arm stays eager.
         launch_mode = "eager"
         run_fwd, run_bwd = step_fwd, step_bwd
 
+        per_graph = next(g for g in (10, 5, 4, 2, 1) if steps % g == 0)
+
         def step_both():
-            step_fwd()
-            step_bwd()
+            for _ in range(per_graph):
+                step_fwd()
+                step_bwd()
 
         run_step = step_both
         if (not seq_sharded or peer_ex is not None) and not args.no_graph:
@@ -518,7 +524,7 @@ def main():
                 from flashy_linear_attention_b200.graphs import capture_step
                 g_fwd, g_bwd, g_step = capture_step(step_fwd), capture_step(step_bwd), capture_step(step_both)
                 run_fwd, run_bwd, run_step = g_fwd, g_bwd, g_step
-                launch_mode = "one CUDA graph replay per step"
+                launch_mode = f"CUDA graph replay, {per_graph} steps per graph"
                 for _ in range(3):
                     run_fwd(); run_bwd(); run_step()
                 barrier()
@@ -530,7 +536,7 @@ def main():
         barrier()
         t_region0 = time.time()
         t0_ev.record(stream)
-        for i in range(steps):
+        for i in range(steps // per_graph):
             run_step()
         t1_ev.record(stream)
         barrier()
@@ -786,8 +792,8 @@ def main():
                 "peak_source": peak_src,
                 "algorithmic_bytes_per_step": fwd_b + bwd_b,
                 "traffic": traffic,
-                "traffic_source": ("ncu DRAM byte count of one step of this workload, captured separately; a constant, "
-                                   "not measured in this run" if traffic is not None else None),
+                "traffic_source": ("ncu DRAM byte count of the two launches at half the sequence length, doubled; a "
+                                   "constant, not measured in this run" if traffic is not None else None),
                 "fwd": {"ms": fwd_ms, "GBps": fwd_b / (fwd_ms * 1e-3) / 1e9, "frac": fwd_b / (fwd_ms * 1e-3) / 1e9 / peak,
                         "Mtokens_per_s": global_batch * N / (fwd_ms * 1e-3) / 1e6},
                 "bwd": {"ms": bwd_ms, "GBps": bwd_b / (bwd_ms * 1e-3) / 1e9, "frac": bwd_b / (bwd_ms * 1e-3) / 1e9 / peak},

@@ -959,6 +959,36 @@ int run_wide_c(const Product& pd, int B, int H, int N, int da, int dc, int32_t* 
   return run_products(slices, n, B, H, N, da, 128, /*segments=*/1, nullptr, 0, status, stream, dev);
 }
 
+// a, b wider than 128 columns AND c, out wider than 64: the output columns are independent, so
+// every 64-column slice of c/out is one launch of the wide-a kernel, which accumulates the whole
+// a/b width in fp32 on chip (LinearAttention with head dims up to 256 on both sides,
+// flashlinear/kernels/linear_attn_kernels.py:316-322, and beyond).
+bool is_wide_both(int da, int dc) {
+  return da > 128 && da <= kWideMaxDim && dc > kWideNarrowDim && dc <= kWideMaxDim;
+}
+int run_wide_both(const Product& pd, int B, int H, int N, int da, int dc, int32_t* status,
+                  cudaStream_t stream) {
+  if (!is_wide_both(da, dc)) return FLA_ERR_UNSUPPORTED;
+  for (int c0 = 0; c0 < dc; c0 += kWideNarrowDim) {
+    Product sl = pd;
+    sl.c.ptr = static_cast<const char*>(pd.c.ptr) + static_cast<size_t>(c0) * 2;
+    sl.out.ptr = static_cast<const char*>(pd.out.ptr) + static_cast<size_t>(c0) * 2;
+    sl.c.dim = sl.out.dim = (dc - c0 < kWideNarrowDim) ? dc - c0 : kWideNarrowDim;
+    const int rc = run_wide_a(sl, B, H, N, da, sl.c.dim, status, stream);
+    if (rc) return rc;
+  }
+  return FLA_OK;
+}
+
+// One product of any supported head-dim pair without running-state arguments.
+int run_wide_any(const Product& pd, int B, int H, int N, int da, int dc, int32_t* status,
+                 cudaStream_t stream, const DeviceInfo& dev) {
+  if (is_wide_a(da, dc)) return run_wide_a(pd, B, H, N, da, dc, status, stream);
+  if (is_wide_c(da, dc)) return run_wide_c(pd, B, H, N, da, dc, status, stream, dev);
+  if (is_wide_both(da, dc)) return run_wide_both(pd, B, H, N, da, dc, status, stream);
+  return FLA_ERR_UNSUPPORTED;
+}
+
 int check_common(const FlaArgs* a, DeviceInfo** dev) {
   if (a == nullptr) return FLA_ERR_INVALID;
   // The launch checks below read the thread's last-error slot; drop whatever an earlier,
@@ -1104,9 +1134,9 @@ int fla_sm100_fwd(const FlaArgs* a) {
   p.ext_init = a->s_init;
   p.ext_final = a->s_final;
   p.ext_trans = 0;
-  if (is_wide_a(a->dk, a->dv))
-    return run_wide_a(p, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->status,
-                      static_cast<cudaStream_t>(a->stream));
+  if (a->dk > 128 || a->dv > 128)
+    return run_wide_any(p, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->status,
+                        static_cast<cudaStream_t>(a->stream), *dev);
   if (a->seg_states != nullptr && a->segment_states_ready == 0) {
     SegPlan f, b;
     const size_t need = seg_states_bytes(a, dev->sm_count, &f, &b);
@@ -1161,15 +1191,19 @@ int fla_sm100_bwd(const FlaArgs* a) {
   pk.ext_final = nullptr;
   pk.ext_trans = 1;
 
-  if (is_wide_a(a->dk, a->dv)) {
-    // SmallVHD shapes: dQ and dK have the wide head dim on the output side, dV on the a/b side.
+  if (a->dk > 128 || a->dv > 128) {
+    // Head dims above the 128-wide tiles (SmallVHD shapes: dQ and dK have the wide head dim on the
+    // output side, dV on the a/b side; both sides wide: all three through the wide-a kernel).
     if (a->s_init || a->r_init || a->r_final || a->s_last) return FLA_ERR_UNSUPPORTED;
-    if ((rc = run_wide_c(pq, a->batch, a->heads, a->seqlen, a->dv, a->dk, a->status, stream, *dev)))
-      return rc;
-    if ((rc = run_wide_c(pk, a->batch, a->heads, a->seqlen, a->dv, a->dk, a->status, stream, *dev)))
-      return rc;
-    rc = run_wide_a(pv, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->status, stream);
-    return rc;
+    auto any = [&](const Product& pd, int da, int dc) {
+      if (da <= 128 && dc <= 128)
+        return run_products(&pd, 1, a->batch, a->heads, a->seqlen, da, dc, a->segments, a->workspace,
+                            a->workspace_bytes, a->status, stream, *dev);
+      return run_wide_any(pd, a->batch, a->heads, a->seqlen, da, dc, a->status, stream, *dev);
+    };
+    if ((rc = any(pq, a->dv, a->dk))) return rc;
+    if ((rc = any(pk, a->dv, a->dk))) return rc;
+    return any(pv, a->dk, a->dv);
   }
   const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
   if (a->seg_states != nullptr && a->s_last != nullptr && single_sweep_allowed(nchunks)) {
@@ -1255,10 +1289,10 @@ int fla_sm100_fwd_static_scratch(const FlaArgs* a) {
   p.ext_init = a->s_init;
   p.ext_final = a->s_final;
   p.ext_trans = 0;
-  // q/k wider than 128 with a narrow v: that kernel never splits the sequence and uses no scratch
-  if (is_wide_a(a->dk, a->dv))
-    return run_wide_a(p, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->status,
-                      static_cast<cudaStream_t>(a->stream));
+  // head dims above 128: those kernels never split the sequence and use no scratch
+  if (a->dk > 128 || a->dv > 128)
+    return run_wide_any(p, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->status,
+                        static_cast<cudaStream_t>(a->stream), *dev);
   // How much scratch this shape needs with the segment count the call will use.
   const int nchunks = (a->seqlen + fla::kChunk - 1) / fla::kChunk;
   int nseg = a->segments > 0 ? a->segments
@@ -1572,12 +1606,9 @@ int fla_sm100_product(const FlaArgs* a, int anticausal) {
   p.ext_init = a->s_init;
   p.ext_final = a->s_final;
   p.ext_trans = 0;
-  if (is_wide_a(a->dk, a->dv))
-    return run_wide_a(p, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->status,
-                      static_cast<cudaStream_t>(a->stream));
-  if (is_wide_c(a->dk, a->dv))
-    return run_wide_c(p, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->status,
-                      static_cast<cudaStream_t>(a->stream), *dev);
+  if (a->dk > 128 || a->dv > 128)
+    return run_wide_any(p, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->status,
+                        static_cast<cudaStream_t>(a->stream), *dev);
   return run_products(&p, 1, a->batch, a->heads, a->seqlen, a->dk, a->dv, a->segments,
                       a->workspace, a->workspace_bytes, a->status,
                       static_cast<cudaStream_t>(a->stream), *dev);

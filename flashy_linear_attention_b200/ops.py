@@ -18,8 +18,8 @@ from . import _lib
 from ._lib import FlaArgs, FlaTensor
 
 KERNEL_HEAD_DIM = 128  # widest head-dim tile of the main kernel
-WIDE_HEAD_DIM = 384    # widest q/k head dim of the wide (SmallVHD) kernel ...
-WIDE_NARROW_DIM = 64   # ... which takes v head dims up to this; other shapes are assembled from slices
+WIDE_HEAD_DIM = 384    # widest head dim (either side) that one library call covers
+WIDE_NARROW_DIM = 64   # c/out width of one launch of the wide (SmallVHD) kernel
 MAX_HEAD_DIM = 256     # cap of LinearAttention, as in the reference (linear_attn_kernels.py:322)
 MAX_HEAD_DIM_QK_SMALLV = 512  # cap of q/k for LinearAttentionSmallVHD (273-dim Taylor features fit)
 
@@ -232,17 +232,16 @@ def _product_call(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, out: torch.
 
 def _native_dims(da: int, dc: int) -> bool:
     """Head-dim pairs (a/b side, c/out side) that one library call covers."""
-    return (da <= KERNEL_HEAD_DIM and dc <= KERNEL_HEAD_DIM) or \
-           (KERNEL_HEAD_DIM < da <= WIDE_HEAD_DIM and dc <= WIDE_NARROW_DIM) or \
-           (da <= KERNEL_HEAD_DIM and KERNEL_HEAD_DIM < dc <= WIDE_HEAD_DIM)
+    return da <= WIDE_HEAD_DIM and dc <= WIDE_HEAD_DIM
 
 
 def _product_sliced(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, like: torch.Tensor, anticausal: bool) -> torch.Tensor:
-    """Causal product for head dims above the kernels' 128-wide tiles, by linearity: output columns
-    are independent (slices of c), and (a_i . b_j) is the sum over slices of the a/b head dim, so
-    the partial products of those slices are added. Each partial product leaves its kernel rounded
-    to bf16; the sum of the (at most two) partials is formed in fp32 and rounded once more, so a
-    result with both head dims above 128 carries up to three bf16 roundings instead of one."""
+    """Causal product for any head dims. Up to 384 on either side the library takes the call as it
+    is (128-wide tiles; a/b wider: the wide kernel, which accumulates the whole a/b width on chip;
+    c/out wider: independent column slices). Beyond that the product is assembled here by
+    linearity: output columns are independent (slices of c), and (a_i . b_j) is the sum over
+    slices of the a/b head dim, so the partial products of those slices are added. Each partial
+    product leaves its kernel rounded to bf16; their sum is formed in fp32 and rounded once more."""
     av, bv, cv = _kernel_view(a), _kernel_view(b), _kernel_view(c)
     da, dc = a.shape[-1], c.shape[-1]
     W = KERNEL_HEAD_DIM
@@ -338,7 +337,7 @@ def causal_dot_product_bwd(
     _check_inputs(grad_output, q, k, v, allow_half=True)
     B, H, N, dk = q.shape
     dv = v.shape[-1]
-    wide = KERNEL_HEAD_DIM < dk <= WIDE_HEAD_DIM and dv <= WIDE_NARROW_DIM
+    wide = max(dk, dv) > KERNEL_HEAD_DIM and max(dk, dv) <= WIDE_HEAD_DIM  # one library call covers it
     if wide and any(t is not None for t in (s_init, r_init, r_final, s_last)):
         raise NotImplementedError("running-state arguments need head dims <= 128")
     if (dk > KERNEL_HEAD_DIM or dv > KERNEL_HEAD_DIM) and not wide:

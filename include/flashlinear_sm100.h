@@ -133,7 +133,13 @@ typedef struct FlaArgs {
 #define FLA_DEBUG_WITHHOLD_FIRST_TILE 1u
 /* Segmented calls normally run as ONE cooperative launch when all their CTAs fit the GPU at once
  * (see fla_sm100_seg_states_bytes). This bit keeps the older three-launch form (state pass, scan,
- * product pass), for comparisons. */
+ * product pass), for comparisons.
+ * The CTAs of such a launch meet at barriers whose words come from a pool of 64 sets inside the
+ * library, handed out round-robin per launch (a captured launch keeps the set it was captured
+ * with). Launches in one stream never overlap; launches that do run at the same time on one GPU
+ * (several streams) must not hold the same set, i.e. must not be 64 or a multiple of 64 fused
+ * launches apart. A process that replays many captured graphs on concurrent streams should set
+ * this bit for all but one of the streams. */
 #define FLA_DEBUG_NO_FUSED_SEGMENTS 2u
 /* The backward uses s_last (dQ in the same end-to-start sweep as dK and dV) only for sequences
  * longer than 2048 tokens; on shorter ones that form is a little less accurate than the

@@ -155,3 +155,49 @@ def test_host_pipeline_has_no_cpu_fallback():
 
     with pytest.raises(RuntimeError, match="CUDA"):
         HostPipeline("cpu")
+
+
+def test_segment_planning_queries_without_a_gpu():
+    """How a call will be split is host arithmetic (148 SMs assumed when no device answers): the
+    queries that size the caller's scratch must agree with each other for the shapes of the
+    benchmark and its per-GPU shares."""
+    from flashy_linear_attention_b200 import _lib
+    from flashy_linear_attention_b200._lib import FlaArgs
+
+    lib = _lib.load()
+
+    def query(B, H, N, dk, dv, segments=0):
+        a = FlaArgs()
+        a.batch, a.heads, a.seqlen, a.dk, a.dv, a.segments = B, H, N, dk, dv, segments
+        return {
+            "seg_fwd": lib.fla_sm100_auto_segments(ctypes.byref(a), 0),
+            "seg_bwd": lib.fla_sm100_auto_segments(ctypes.byref(a), 1),
+            "ws_fwd": lib.fla_sm100_workspace_bytes(ctypes.byref(a), 0),
+            "ws_bwd": lib.fla_sm100_workspace_bytes(ctypes.byref(a), 1),
+            "states": lib.fla_sm100_seg_states_bytes(ctypes.byref(a)),
+            "uses_final": lib.fla_sm100_bwd_uses_final_state(ctypes.byref(a)),
+        }
+
+    # the whole benchmark job: 128 heads fill the GPU, nothing is split, the backward sweeps once
+    full = query(4, 32, 8192, 128, 128)
+    assert full["seg_fwd"] == 1 and full["seg_bwd"] == 1
+    assert full["ws_fwd"] == 0 and full["ws_bwd"] == 0 and full["states"] == 0
+    assert full["uses_final"] == 1
+    # its share on one of 8 GPUs: 16 heads, forward in 8 segments, backward in 3, both from one launch
+    share = query(1, 16, 8192, 128, 128)
+    assert share["seg_fwd"] == 8 and share["seg_bwd"] == 3
+    assert share["states"] == 16 * 7 * 128 * 128 * 4      # one boundary state per segment but the first
+    assert share["ws_fwd"] >= 16 * 8 * 128 * 128 * 4 and share["ws_bwd"] >= 3 * 16 * 3 * 128 * 128 * 4
+    assert share["uses_final"] == 1
+    # scratch states are padded to the kernel's tile: head dim 96 is sized like 128
+    assert query(1, 16, 8192, 96, 96)["states"] == share["states"]
+    assert query(1, 16, 8192, 64, 64)["states"] == 16 * 7 * 64 * 64 * 4
+    # a long sequence whose even split (57 chunks) would not divide it gets equal segments (64)
+    long = query(1, 16, 65536, 128, 128)
+    assert long["states"] == 16 * 7 * 128 * 128 * 4
+    # short sequences keep the two-direction backward; dk != dv and wide heads have no boundary states
+    assert query(1, 16, 2048, 128, 128)["uses_final"] == 0
+    assert query(1, 16, 8192, 128, 64)["states"] == 0
+    assert query(1, 16, 8192, 256, 64)["states"] == 0
+    # an explicit segment count is honoured
+    assert query(1, 4, 8192, 128, 128, segments=4)["seg_fwd"] == 4

@@ -140,13 +140,15 @@ def test_seeded_inputs_against_oracle(shape):
 
 @pytest.mark.parametrize("shape", [(1, 2, 256, 256, 256), (1, 2, 192, 200, 136), (2, 2, 256, 273, 64),
                                    (1, 1, 128, 384, 64), (1, 2, 640, 273, 32), (2, 1, 320, 144, 16),
-                                   (1, 2, 1152, 256, 64), (1, 1, 448, 330, 64)],
+                                   (1, 2, 1152, 256, 64), (1, 1, 448, 330, 64), (1, 2, 384, 256, 128),
+                                   (2, 2, 512, 160, 192), (1, 1, 320, 96, 256), (1, 1, 256, 384, 384)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_head_dims_above_the_kernel_tile(shape):
     """Head dims above 128 (the reference allows up to 256, flashlinear/kernels/
-    linear_attn_kernels.py:322; benchmark configuration 4 uses 273 Taylor features): q/k up to 384
-    wide with v up to 64 run in the wide kernel (forward, dV) and as 128-column output slices
-    (dQ, dK); other shapes are assembled from 128-wide slices. Same tolerance."""
+    linear_attn_kernels.py:322; benchmark configuration 4 uses 273 Taylor features), every
+    combination up to 384 inside ONE library call per pass: a/b wider than 128 run in the wide
+    kernel, whose c/out side is cut into 64-column launches when it is wider than that; c/out
+    wider than 128 with a/b at most 128 run as 128-column slices of one grid. Same tolerance."""
     B, H, N, dk, dv = shape
     rng = np.random.default_rng(dk * 1000 + dv)
     # scaled so that the scores stay O(1) at these widths
