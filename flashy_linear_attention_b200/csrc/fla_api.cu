@@ -895,12 +895,14 @@ int run_state(const Operand& bop, const Operand& cop, int B, int H, int N, int d
 
 // Head dims above the 128-wide tiles of fla_chunk_kernel.
 constexpr int kWideMaxDim = 384;   // widest a/b (wide-a) or c/out (wide-c) head dim
-constexpr int kWideNarrowDim = 64; // widest c/out of the wide-a kernel
+constexpr int kWideNarrowDim = 64; // c/out columns one CTA of the wide-a kernel computes
 
-bool is_wide_a(int da, int dc) { return da > 128 && da <= kWideMaxDim && dc <= kWideNarrowDim; }
+bool is_wide_a(int da, int dc) { return da > 128 && da <= kWideMaxDim && dc <= kWideMaxDim; }
 bool is_wide_c(int da, int dc) { return da <= 128 && dc > 128 && dc <= kWideMaxDim; }
 
-// a, b wider than 128 columns, c and out at most 64: fla_wide_kernel, one CTA per (batch, head).
+// a, b wider than 128 columns: fla_wide_kernel, one CTA per (64-column slice of c/out, batch, head).
+// It accumulates the whole a/b width in fp32 on chip; c/out may be as wide as a/b (LinearAttention
+// with head dims up to 256 on both sides, flashlinear/kernels/linear_attn_kernels.py:316-322).
 int run_wide_a(const Product& pd, int B, int H, int N, int da, int dc, int32_t* status,
                cudaStream_t stream) {
   if (!is_wide_a(da, dc)) return FLA_ERR_UNSUPPORTED;
@@ -923,7 +925,8 @@ int run_wide_a(const Product& pd, int B, int H, int N, int da, int dc, int32_t* 
   wp.status = status;
   wp.wait_limit_kcycles = g_wait_limit_kcycles;
   wp.debug_withhold = g_debug_withhold;
-  const dim3 grid(1, 1, B * H);
+  // one CTA per (64-column slice of c/out, batch, head)
+  const dim3 grid((dc + kWideNarrowDim - 1) / kWideNarrowDim, 1, B * H);
   if (da <= 256)
     fla::fla_wide_kernel<2><<<grid, fla::kWideThreads, fla::WideCfg<2>::SMEM_BYTES, stream>>>(wp);
   else
@@ -959,33 +962,11 @@ int run_wide_c(const Product& pd, int B, int H, int N, int da, int dc, int32_t* 
   return run_products(slices, n, B, H, N, da, 128, /*segments=*/1, nullptr, 0, status, stream, dev);
 }
 
-// a, b wider than 128 columns AND c, out wider than 64: the output columns are independent, so
-// every 64-column slice of c/out is one launch of the wide-a kernel, which accumulates the whole
-// a/b width in fp32 on chip (LinearAttention with head dims up to 256 on both sides,
-// flashlinear/kernels/linear_attn_kernels.py:316-322, and beyond).
-bool is_wide_both(int da, int dc) {
-  return da > 128 && da <= kWideMaxDim && dc > kWideNarrowDim && dc <= kWideMaxDim;
-}
-int run_wide_both(const Product& pd, int B, int H, int N, int da, int dc, int32_t* status,
-                  cudaStream_t stream) {
-  if (!is_wide_both(da, dc)) return FLA_ERR_UNSUPPORTED;
-  for (int c0 = 0; c0 < dc; c0 += kWideNarrowDim) {
-    Product sl = pd;
-    sl.c.ptr = static_cast<const char*>(pd.c.ptr) + static_cast<size_t>(c0) * 2;
-    sl.out.ptr = static_cast<const char*>(pd.out.ptr) + static_cast<size_t>(c0) * 2;
-    sl.c.dim = sl.out.dim = (dc - c0 < kWideNarrowDim) ? dc - c0 : kWideNarrowDim;
-    const int rc = run_wide_a(sl, B, H, N, da, sl.c.dim, status, stream);
-    if (rc) return rc;
-  }
-  return FLA_OK;
-}
-
 // One product of any supported head-dim pair without running-state arguments.
 int run_wide_any(const Product& pd, int B, int H, int N, int da, int dc, int32_t* status,
                  cudaStream_t stream, const DeviceInfo& dev) {
   if (is_wide_a(da, dc)) return run_wide_a(pd, B, H, N, da, dc, status, stream);
   if (is_wide_c(da, dc)) return run_wide_c(pd, B, H, N, da, dc, status, stream, dev);
-  if (is_wide_both(da, dc)) return run_wide_both(pd, B, H, N, da, dc, status, stream);
   return FLA_ERR_UNSUPPORTED;
 }
 

@@ -78,6 +78,10 @@ fla_wide_kernel(const __grid_constant__ WideParams p) {
   const int bh = blockIdx.z;
   const int h = bh % p.heads;
   const int b = bh / p.heads;
+  // c and out wider than 64 columns: block x takes columns [64 x, 64 x + 64). The slices of a head
+  // are neighbours in launch order, stream the same a, b tiles at the same time and share them in
+  // L2; columns beyond the tensors' width are zero-filled on load and dropped on store by the TMA.
+  const int c_col0 = static_cast<int>(blockIdx.x) * 64;
 
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
@@ -175,7 +179,7 @@ fla_wide_kernel(const __grid_constant__ WideParams p) {
       if (leader) {
         ptx::mbar_expect_tx(cfull_bar(cs), kWideGroupBytes);
         if (!(p.debug_withhold && i == 0))
-          ptx::tma_load_4d(c_addr + cs * kWideGroupBytes, &p.c, cfull_bar(cs), 0, tok, h, b);
+          ptx::tma_load_4d(c_addr + cs * kWideGroupBytes, &p.c, cfull_bar(cs), c_col0, tok, h, b);
       }
       for (int t = 0; t < NT; ++t) {
         const int groups = pair_groups(t);  // a group that is all padding is not loaded
@@ -397,7 +401,7 @@ fla_wide_kernel(const __grid_constant__ WideParams p) {
       __syncwarp();
       const int tok = mem_chunk(i) * kWideChunk + quad * 32;
       if (lane == 0 && tok < p.n_tokens) {
-        ptx::tma_store_4d(&p.o, ost_addr + quad * (32 * 128), 0, tok, h, b);
+        ptx::tma_store_4d(&p.o, ost_addr + quad * (32 * 128), c_col0, tok, h, b);
         ptx::bulk_commit_group();
       }
     }

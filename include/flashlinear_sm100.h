@@ -242,15 +242,17 @@ int fla_sm100_enable_peer_access(int peer_device);
  * tokens after / up to this call's tokens). fla_sm100_fwd is this product of (q, k, v); the
  * gradients of flashlinear/kernels/linear_attn_kernels.py:179-197 and :291-299 are
  * dQ = product(dO, v, k), dV = anticausal product(k, q, dO), dK = anticausal product(v, dO, q).
- * The Python layer uses it to assemble head dims above 128 from 128-wide slices. Workspace: as for
- * pass 0. */
+ * The Python layer uses it to assemble head dims above 384 from slices. Workspace: as for pass 0. */
 int fla_sm100_product(const FlaArgs* args, int anticausal);
 
 /* Head dims above 128 (the SmallVHD shapes of flashlinear/kernels/linear_attn_kernels_smallv_hd.py:
- * q, k wide, v narrow): fla_sm100_fwd, fla_sm100_bwd and fla_sm100_product also accept
- *   dk in (128, 384] with dv <= 64   q/k tiles streamed in 128-column pieces by a dedicated kernel,
- *   dk <= 128 with dv in (128, 384]  (fla_sm100_product only) output columns computed in 128-wide slices,
- * without running-state arguments, segments or workspace. Row strides must still be multiples of
+ * q, k wide, v narrow; LinearAttention with head dims up to 256, linear_attn_kernels.py:316-322):
+ * fla_sm100_fwd, fla_sm100_bwd and fla_sm100_product accept every dk, dv up to 384 (bf16):
+ *   dk in (128, 384]                  q/k tiles streamed in 128-column pieces by a dedicated kernel, one
+ *                                     CTA per 64-column slice of v / o (one slice when dv <= 64),
+ *   dk <= 128 with dv in (128, 384]   output columns computed in 128-wide slices of one grid,
+ * (for the backward the same rules apply to each of the three gradient products with its own
+ * operand widths), without running-state arguments, segments or workspace. Row strides must still be multiples of
  * 16 bytes; a contiguous tensor with an odd head dim (273) is first copied to padded rows: */
 /* dst[r][0..dpad) = src[r][0..d) followed by zeros; src and dst contiguous bf16, dpad a multiple of 8.
  * The reference pads in registers instead (boundary_check / padding_option="zero",
