@@ -236,7 +236,7 @@ def run_reference(args, rank, shape, name, emit):
         "impl": "reference",
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": t * 1e3,
-        "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"{name}: B={B} H={H} N={N} dk={dk} dv={dv}",
                    "sample": sample},
@@ -753,7 +753,7 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "bf16",
+            "scaling": "strong" if strong else args.scaling, "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {
                 "workload": f"{wname}: {'LinearAttentionSmallVHD' if dk != dv else 'LinearAttention'} "

@@ -634,14 +634,16 @@ int launch_template(int tmpl, const KernelParams& kp, dim3 grid, cudaStream_t st
   return FLA_ERR_UNSUPPORTED;
 }
 
+// Which set of barrier words the next fused launch of this process gets (round-robin).
+std::atomic<unsigned> g_next_barrier_slot{0};
+
 // Cooperative launch (all CTAs resident at once, or the launch fails) of the fused segmented form.
 template <int D>
 int launch_fused_kernel(const KernelParams& kp_in, dim3 grid, cudaStream_t stream) {
-  static std::atomic<unsigned> next_slot{0};
   KernelParams kp = kp_in;
   kp.wait_limit_kcycles = g_wait_limit_kcycles;
   kp.debug_withhold = g_debug_withhold;
-  kp.bar_slot = next_slot.fetch_add(1, std::memory_order_relaxed) % fla::kGridBarSlots;
+  kp.bar_slot = g_next_barrier_slot.fetch_add(1, std::memory_order_relaxed) % fla::kGridBarSlots;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = grid;
