@@ -383,7 +383,8 @@ __device__ __noinline__ bool converter_prologue(const KernelParams& p, const Pro
         // same access patterns as below with every offset an immediate and no bounds tests: a
         // quarter of the instructions, which is what this once-per-CTA code costs in
         if (trans) {
-          const float* ptr = base + static_cast<size_t>(cb) * 32 * DK + row;
+          // rows beyond the state (DK = 64: the upper two warp quadrants) load row 0 and are zeroed below
+          const float* ptr = base + static_cast<size_t>(cb) * 32 * DK + (row < DK ? row : 0);
           ptx::static_for<32>([&](auto j) {
             constexpr int J = decltype(j)::value;
             r[J] = ptx::ld_global_cg_b32_at<J * DK * 4>(ptr);

@@ -174,3 +174,52 @@ def test_fused_forward_with_running_state_arguments():
     ops.check_status(DEV)
     for a, b, w in zip(g1, g2, gw):
         assert _frob(torch.cat([a, b], dim=2), w) < 2e-3
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_random_shapes_segment_counts_and_dtypes_match_the_unsegmented_kernels(seed):
+    """Seeded random sweep over heads (1 .. 74), chunk counts, ragged lengths, head dims 32 .. 128,
+    automatic and explicit segment counts, bf16 / fp16 and an initial state: whatever form the
+    library picks (fused with or without boundary states, three launches, unsegmented) must agree
+    with the unsegmented kernels on out, dQ, dK, dV and the final state."""
+    import random
+
+    from flashy_linear_attention_b200 import ops
+
+    rng = random.Random(seed)
+    ran = 0
+    for case in range(60):
+        D = rng.choice([64, 128, 128, 96, 32])
+        H = rng.choice([1, 2, 3, 5, 7, 8, 12, 16, 20, 24, 31, 40, 49, 64, 74])
+        N = rng.choice([2, 3, 5, 8, 17, 18, 24, 33, 40, 64, 65]) * 128 - rng.choice([0, 0, 0, 64])
+        if H * N * D > 40e6:
+            continue
+        segments = rng.choice([0, 0, 0, 2, 3, 4, 7, 9])
+        dt = rng.choice([torch.bfloat16, torch.bfloat16, torch.float16])
+        with_init = rng.random() < 0.3
+        gen = torch.Generator(device=DEV).manual_seed(N * 7 + H)
+        q = ((torch.nn.functional.elu(torch.randn(1, H, N, D, device=DEV, generator=gen)) + 1) / D ** 0.5).to(dt)
+        k = (torch.nn.functional.elu(torch.randn(1, H, N, D, device=DEV, generator=gen)) + 1).to(dt)
+        v = torch.randn(1, H, N, D, device=DEV, generator=gen).to(dt)
+        dy = torch.randn(1, H, N, D, device=DEV, generator=gen).to(dt)
+        s_init = torch.randn(H, D, D, device=DEV, generator=gen) * 0.1 if with_init else None
+
+        def run(segs, use_states):
+            s_final = torch.empty(H, D, D, dtype=torch.float32, device=DEV)
+            seg_states = ops.segment_states_buffer(q, v, segs) if use_states else None
+            out = ops.causal_dot_product_fwd(q, k, v, s_init=s_init, s_final=s_final, segments=segs,
+                                             seg_states=seg_states)
+            grads = ops.causal_dot_product_bwd(dy, q, k, v, s_init=s_init, s_last=s_final, segments=segs,
+                                               seg_states=seg_states)
+            return (out,) + tuple(grads) + (s_final,)
+
+        got, want = run(segments, True), run(1, False)
+        torch.cuda.synchronize()
+        ops.check_status(DEV)
+        label = (case, H, N, D, segments, str(dt), with_init)
+        for name, a, b in zip(("out", "dq", "dk", "dv"), got, want):
+            assert torch.isfinite(a.float()).all(), (label, name)
+            assert _frob(a, b) < 1.2e-2, (label, name, _frob(a, b))
+        assert _frob(got[4], want[4]) < 1e-4, (label, "s_final", _frob(got[4], want[4]))
+        ran += 1
+    assert ran >= 40
