@@ -159,7 +159,7 @@ class ClockSampler:
         if not sm:  # region shorter than the sampling period: fall back to the whole run
             sm, smax, reasons = parse(False)
             scope = "whole run (timed region shorter than one sample)"
-        return {
+        out = {
             "sm_mhz": statistics.median(sm) if sm else None,
             "sm_min_mhz": min(sm) if sm else None,
             "sm_max_mhz": max(smax) if smax else None,
@@ -167,6 +167,11 @@ class ClockSampler:
             "scope": scope,
             "reasons": sorted(reasons),
         }
+        # SM clock well below its maximum with no throttle reason active: somebody else's clock
+        # lock on a shared host. The number is still reported, with this flag, for a re-measurement.
+        if sm and smax and not reasons and statistics.median(sm) < 0.9 * max(smax):
+            out["suspect"] = "sm clock below 90 % of max with no throttle reason active (clock lock?)"
+        return out
 
 
 def taylor_features(x):
