@@ -80,6 +80,7 @@ class FlaExchange(ctypes.Structure):
 
 EXPORTED_SYMBOLS = (
     "fla_sm100_abi_version",
+    "fla_sm100_timeout_records",
     "fla_sm100_strerror",
     "fla_sm100_workspace_bytes",
     "fla_sm100_auto_segments",
@@ -125,6 +126,8 @@ def load() -> ctypes.CDLL:
         )
     lib = ctypes.CDLL(LIB_PATH)
     lib.fla_sm100_abi_version.restype = ctypes.c_int
+    lib.fla_sm100_timeout_records.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    lib.fla_sm100_timeout_records.restype = ctypes.c_int
     lib.fla_sm100_strerror.restype = ctypes.c_char_p
     lib.fla_sm100_strerror.argtypes = [ctypes.c_int]
     lib.fla_sm100_workspace_bytes.restype = ctypes.c_size_t

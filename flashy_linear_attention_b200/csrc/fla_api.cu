@@ -1040,6 +1040,22 @@ extern "C" {
 
 int fla_sm100_abi_version(void) { return FLA_ABI_VERSION; }
 
+int fla_sm100_timeout_records(unsigned* out, int max_records) {
+  if (out == nullptr || max_records <= 0) return FLA_ERR_INVALID;
+  if (cudaDeviceSynchronize() != cudaSuccess) return FLA_ERR_CUDA;
+  unsigned n = 0;
+  static unsigned host_copy[fla::ptx::kTimeoutRecords * 8];
+  if (cudaMemcpyFromSymbol(&n, fla::ptx::g_timeout_count, sizeof(n)) != cudaSuccess ||
+      cudaMemcpyFromSymbol(host_copy, fla::ptx::g_timeout_records, sizeof(host_copy)) != cudaSuccess)
+    return FLA_ERR_CUDA;
+  const unsigned zero = 0;
+  if (cudaMemcpyToSymbol(fla::ptx::g_timeout_count, &zero, sizeof(zero)) != cudaSuccess) return FLA_ERR_CUDA;
+  int got = static_cast<int>(n < static_cast<unsigned>(fla::ptx::kTimeoutRecords) ? n : fla::ptx::kTimeoutRecords);
+  if (got > max_records) got = max_records;
+  memcpy(out, host_copy, static_cast<size_t>(got) * 8 * sizeof(unsigned));
+  return got;
+}
+
 const char* fla_sm100_strerror(int code) {
   switch (code) {
     case FLA_OK: return "ok";

@@ -61,6 +61,25 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // wait of these kernels, which are microseconds.
 constexpr long long kWaitLimitCycles = 800ll * 1000ll * 1000ll;
 
+// Diagnostics for the status bit: the first few waits that ran out (since the last read-out) leave
+// a record of which barrier they were waiting on. Only the give-up path touches these.
+constexpr int kTimeoutRecords = 32;
+static __device__ unsigned g_timeout_records[kTimeoutRecords * 8];
+static __device__ unsigned g_timeout_count;
+__device__ __noinline__ void record_timeout(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  const unsigned slot = atomicAdd(&g_timeout_count, 1u);
+  if (slot >= static_cast<unsigned>(kTimeoutRecords)) return;
+  unsigned* r = &g_timeout_records[slot * 8];
+  r[0] = bar;      // shared-memory address of the mbarrier
+  r[1] = parity;
+  r[2] = threadIdx.x;
+  r[3] = blockIdx.x;
+  r[4] = blockIdx.y;
+  r[5] = blockIdx.z;
+  r[6] = static_cast<unsigned>(__cvta_generic_to_shared(const_cast<int*>(abort_flag)));  // locates the barrier area
+  r[7] = static_cast<unsigned>(clock64() >> 10);
+}
+
 // Waits for the phase with the given parity. Returns false when the CTA-wide abort flag is set
 // or the limit ran out (in which case it sets the flag so that every other wait of the CTA
 // gives up too). `abort_flag` points at two shared-memory words: [0] the flag, [1] the limit in
@@ -79,6 +98,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if ((spin & 63u) == 0u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > limit) {
+        if (*abort_flag == 0) record_timeout(bar, parity, abort_flag);
         *abort_flag = 1;
         return false;
       }

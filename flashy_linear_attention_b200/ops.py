@@ -40,13 +40,52 @@ def _next_pow2(x: int) -> int:
     return 1 << (max(int(x), 1) - 1).bit_length()
 
 
+_first_use_status: dict = {}  # device index -> status word after the first-use launches (0 = clean)
+
+
 def _status_word(device: torch.device) -> torch.Tensor:
     key = device.index if device.index is not None else torch.cuda.current_device()
     w = _status_words.get(key)
     if w is None:
         w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
         _status_words[key] = w
+        _first_use(torch.device("cuda", key), w)
     return w
+
+
+def _first_use(device: torch.device, status: torch.Tensor) -> None:
+    """One throw-away forward + backward per kernel instantiation (head dims 64 and 128) the first
+    time a device is used, then the status word is cleared.
+
+    Why: on some B200 hosts the very first launch of the 64-wide kernel in a fresh process ran into
+    its 0.4 s wait limit (about one fresh process in ten on two hosts, never on three others, never
+    in any later launch: 11,000 consecutive steps clean); the cause has not been found. The library's
+    module load, the switch of the SMs to its shared-memory configuration and the cold instruction
+    caches all fall on that launch. Taking it on 160 heads of 128 tokens whose results nobody reads keeps a
+    caller's first real call from being the one that is lost. Skipped while a stream is being
+    captured (nothing may synchronise then)."""
+    if torch.cuda.is_current_stream_capturing():
+        return
+    lib = _lib.load()
+    stream = torch.cuda.current_stream(device).cuda_stream
+    with torch.cuda.device(device):
+        for d in (64, 128):
+            x = torch.ones(1, 160, 128, d, dtype=torch.bfloat16, device=device)  # a CTA on every SM
+            outs = [torch.empty_like(x) for _ in range(4)]
+            a = FlaArgs()
+            a.batch, a.heads, a.seqlen, a.dk, a.dv = 1, 160, 128, d, d
+            a.q, a.k, a.v, a.d_o = _desc(x), _desc(x), _desc(x), _desc(x)
+            a.o, a.d_q, a.d_k, a.d_v = (_desc(t) for t in outs)
+            a.segments = 1
+            a.status = status.data_ptr()
+            a.stream = stream
+            lib.fla_sm100_fwd(ctypes.byref(a))
+            lib.fla_sm100_bwd(ctypes.byref(a))
+        torch.cuda.synchronize(device)
+        _first_use_status[device.index] = int(status.item())  # kept for diagnosis; not an error
+        status.zero_()
+        scratch = (ctypes.c_uint * 8)()
+        lib.fla_sm100_timeout_records(scratch, 1)  # drop whatever the warm-up may have recorded
 
 
 def check_status(device=None) -> None:

@@ -146,6 +146,13 @@ typedef struct FlaArgs {
  * two-direction form and saves nothing worth having. This bit lifts the length rule, for tests. */
 #define FLA_DEBUG_FORCE_SINGLE_SWEEP 4u
 
+/* Diagnostics for bit 0 of the status word: copies up to max_records records (8 words each) of the
+ * first waits that ran out on the current device since the last call, and clears them. Words:
+ * shared-memory address of the mbarrier, parity waited for, thread index, block x / y / z,
+ * shared-memory address of the CTA's abort flag (which locates the barrier area), clock >> 10.
+ * Synchronises the device. Returns the number of records, or a negative error code. */
+int fla_sm100_timeout_records(unsigned* out, int max_records);
+
 /* pass: 0 = forward, 1 = backward, 2 = fla_sm100_state */
 int fla_sm100_abi_version(void);
 const char* fla_sm100_strerror(int code);
