@@ -130,6 +130,17 @@ def test_mbarrier_wait_that_runs_out_sets_the_status_bit(dims):
     assert lib.fla_sm100_fwd(ctypes.byref(a)) == 0
     torch.cuda.synchronize()
     assert int(status.item()) & 1
+    # the library recorded which waits gave up first: block indices inside the launch's grid, a
+    # thread of the CTA, a barrier inside the CTA's barrier area (just below its abort flag)
+    recs = (ctypes.c_uint * (8 * 32))()
+    n = lib.fla_sm100_timeout_records(recs, 32)
+    assert 1 <= n <= 32
+    for r in range(n):
+        bar, parity, tid, bx, by, bz, flag_addr, _clk = recs[8 * r: 8 * r + 8]
+        assert parity in (0, 1) and tid < 512 and bz < B * H and by == 0
+        if dk <= 128:  # the chunk kernel keeps its abort flag right behind its barriers
+            assert 0 < flag_addr - bar <= 512 and (flag_addr - bar) % 4 == 0
+    assert lib.fla_sm100_timeout_records(recs, 32) == 0  # reading clears them
     with pytest.raises(RuntimeError, match="timed out"):
         ops.check_status(DEV)
     # same arguments without the hook: the call completes and matches the ordinary wrapper
