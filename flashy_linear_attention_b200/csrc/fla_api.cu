@@ -57,7 +57,7 @@ EncodeTiledFn get_encode_fn() {
 thread_local int g_last_launches = 0;
 // Bounded-wait limit (units of 1024 SM cycles, 0 = default) and the wait-timeout test hook of the
 // call in progress on this thread; check_common() sets them from FlaArgs.
-thread_local unsigned g_wait_limit_kcycles = 0;
+thread_local unsigned g_wait_limit_us = 0;
 thread_local int g_debug_withhold = 0;
 thread_local int g_no_fused = 0;  // FLA_DEBUG_NO_FUSED_SEGMENTS: keep the three-launch segmented path
 thread_local int g_force_single_sweep = 0;  // FLA_DEBUG_FORCE_SINGLE_SWEEP
@@ -614,7 +614,7 @@ size_t seg_states_bytes(const FlaArgs* a, int sm_count, SegPlan* fwd_out, SegPla
 template <int D>
 int launch_kernel(const KernelParams& kp_in, dim3 grid, cudaStream_t stream) {
   KernelParams kp = kp_in;
-  kp.wait_limit_kcycles = g_wait_limit_kcycles;
+  kp.wait_limit_us = g_wait_limit_us;
   kp.debug_withhold = g_debug_withhold;
   if (g_half)
     fla::fla_chunk_kernel<D, D, true><<<grid, fla::kThreads, fla::Cfg<D, D>::SMEM_BYTES, stream>>>(kp);
@@ -641,7 +641,7 @@ std::atomic<unsigned> g_next_barrier_slot{0};
 template <int D>
 int launch_fused_kernel(const KernelParams& kp_in, dim3 grid, cudaStream_t stream) {
   KernelParams kp = kp_in;
-  kp.wait_limit_kcycles = g_wait_limit_kcycles;
+  kp.wait_limit_us = g_wait_limit_us;
   kp.debug_withhold = g_debug_withhold;
   kp.bar_slot = g_next_barrier_slot.fetch_add(1, std::memory_order_relaxed) % fla::kGridBarSlots;
   cudaLaunchConfig_t cfg;
@@ -925,7 +925,7 @@ int run_wide_a(const Product& pd, int B, int H, int N, int da, int dc, int32_t* 
   wp.nchunks = (N + fla::kWideChunk - 1) / fla::kWideChunk;
   wp.da = da;
   wp.status = status;
-  wp.wait_limit_kcycles = g_wait_limit_kcycles;
+  wp.wait_limit_us = g_wait_limit_us;
   wp.debug_withhold = g_debug_withhold;
   // one CTA per (64-column slice of c/out, batch, head)
   const dim3 grid((dc + kWideNarrowDim - 1) / kWideNarrowDim, 1, B * H);
@@ -984,12 +984,7 @@ int check_common(const FlaArgs* a, DeviceInfo** dev) {
   if (rc) return rc;
   if ((*dev)->cc_major != 10) return FLA_ERR_DEVICE;
   if (!(*dev)->attr_set[0]) return FLA_ERR_CUDA;
-  g_wait_limit_kcycles = 0;
-  if (a->wait_limit_us != 0) {
-    const unsigned long long cycles =
-        static_cast<unsigned long long>(a->wait_limit_us) * (*dev)->clock_khz / 1000ull;
-    g_wait_limit_kcycles = static_cast<unsigned>(std::min<unsigned long long>((cycles >> 10) + 1, 0x7fffffffull));
-  }
+  g_wait_limit_us = a->wait_limit_us > 0x7fffffffu ? 0x7fffffffu : a->wait_limit_us;
   g_debug_withhold = (a->debug_flags & FLA_DEBUG_WITHHOLD_FIRST_TILE) ? 1 : 0;
   g_no_fused = (a->debug_flags & FLA_DEBUG_NO_FUSED_SEGMENTS) ? 1 : 0;
   g_force_single_sweep = (a->debug_flags & FLA_DEBUG_FORCE_SINGLE_SWEEP) ? 1 : 0;

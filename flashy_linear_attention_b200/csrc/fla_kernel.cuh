@@ -82,7 +82,7 @@ struct KernelParams {
   int st_cols;
   int skip_last_segment;  // mode 1: the last segment's sum is not needed
   int* status;     // device word, bit 0 set when a bounded wait ran out; may be null
-  unsigned wait_limit_kcycles;  // limit of one bounded wait in units of 1024 SM cycles; 0 = default
+  unsigned wait_limit_us;  // limit of one bounded wait in microseconds of the global timer; 0 = default
   int debug_withhold;  // test hook: the producer skips the load of its first tile, so that the
                        // consumers' bounded wait runs out and the status path is exercised
   // ---- fused segments: ONE launch does what mode 1 + the scan kernel + mode 0 do in three.
@@ -618,7 +618,7 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
   // ------------------------------------------------------------------ setup
   if (threadIdx.x == 0) {
     abort_flag[0] = 0;
-    abort_flag[1] = static_cast<int>(p.wait_limit_kcycles);
+    abort_flag[1] = static_cast<int>(p.wait_limit_us);
     for (int s = 0; s < NSLOT; ++s) {
       ptx::mbar_init(full_bar(s), 1);
       // mode 0: every tile is read by two MMA groups, each followed by a tcgen05.commit arrival

@@ -38,7 +38,7 @@ struct WideParams {
   int nchunks;
   int da;            // valid columns of a and b
   int* status;       // device word, bit 0 set when a bounded wait ran out; may be null
-  unsigned wait_limit_kcycles;  // limit of one bounded wait in units of 1024 SM cycles; 0 = default
+  unsigned wait_limit_us;  // limit of one bounded wait in microseconds of the global timer; 0 = default
   int debug_withhold;  // test hook: the first c tile is never loaded, so the waits on it run out
 };
 
@@ -113,7 +113,7 @@ fla_wide_kernel(const __grid_constant__ WideParams p) {
 
   if (threadIdx.x == 0) {
     abort_flag[0] = 0;
-    abort_flag[1] = static_cast<int>(p.wait_limit_kcycles);
+    abort_flag[1] = static_cast<int>(p.wait_limit_us);
     for (int s = 0; s < kWideSlots; ++s) {
       ptx::mbar_init(full_bar(s), 1);
       ptx::mbar_init(empty_bar(s), 1);

@@ -57,9 +57,18 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return done;
 }
 
-// Default limit of one wait in SM clock cycles (about 0.4 s at 2 GHz): far above any legitimate
-// wait of these kernels, which are microseconds.
-constexpr long long kWaitLimitCycles = 800ll * 1000ll * 1000ll;
+// Default limit of one wait: 2 s of the GPU's global timer, far above any legitimate wait of these
+// kernels, which are microseconds. Waits are timed with %globaltimer, not clock64(): a CTA that is
+// preempted (another context's time slice on a shared GPU) may resume on another SM, whose cycle
+// counter has nothing to do with the one read before, and the time it spent switched out must not
+// count against a 0.4 s limit either (a wait of a process's first launch, taken while the previous
+// process's context was still being torn down, did run out that way).
+constexpr unsigned long long kWaitLimitNs = 2000ull * 1000ull * 1000ull;
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 // Diagnostics for the status bit: the first few waits that ran out (since the last read-out) leave
 // a record of which barrier they were waiting on. Only the give-up path touches these.
@@ -77,27 +86,27 @@ __device__ __noinline__ void record_timeout(uint32_t bar, uint32_t parity, volat
   r[4] = blockIdx.y;
   r[5] = blockIdx.z;
   r[6] = static_cast<unsigned>(__cvta_generic_to_shared(const_cast<int*>(abort_flag)));  // locates the barrier area
-  r[7] = static_cast<unsigned>(clock64() >> 10);
+  r[7] = static_cast<unsigned>(global_timer_ns() >> 10);
 }
 
 // Waits for the phase with the given parity. Returns false when the CTA-wide abort flag is set
 // or the limit ran out (in which case it sets the flag so that every other wait of the CTA
 // gives up too). `abort_flag` points at two shared-memory words: [0] the flag, [1] the limit in
-// units of 1024 cycles (0 = kWaitLimitCycles), which the host can shorten for tests.
+// microseconds (0 = kWaitLimitNs), which the host can shorten for tests.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
 #pragma unroll 1
   for (int spin = 0; spin < 64; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
   }
-  const long long t0 = clock64();
-  const unsigned lim_k = static_cast<unsigned>(abort_flag[1]);
-  const long long limit = lim_k ? (static_cast<long long>(lim_k) << 10) : kWaitLimitCycles;
+  const unsigned long long t0 = global_timer_ns();
+  const unsigned lim_us = static_cast<unsigned>(abort_flag[1]);
+  const unsigned long long limit = lim_us ? static_cast<unsigned long long>(lim_us) * 1000ull : kWaitLimitNs;
 #pragma unroll 1
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > limit) {
+      if (global_timer_ns() - t0 > limit) {
         if (*abort_flag == 0) record_timeout(bar, parity, abort_flag);
         *abort_flag = 1;
         return false;
@@ -130,9 +139,9 @@ __device__ __forceinline__ bool grid_barrier(unsigned* bar, unsigned n_ctas, uns
     asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(bar), "r"(0u) : "memory");
     return true;
   }
-  const long long t_start = clock64();
-  const unsigned lim_k = static_cast<unsigned>(abort_flag[1]);
-  const long long limit = lim_k ? (static_cast<long long>(lim_k) << 10) : kWaitLimitCycles;
+  const unsigned long long t_start = global_timer_ns();
+  const unsigned lim_us = static_cast<unsigned>(abort_flag[1]);
+  const unsigned long long limit = lim_us ? static_cast<unsigned long long>(lim_us) * 1000ull : kWaitLimitNs;
 #pragma unroll 1
   for (uint32_t spin = 1;; ++spin) {
     unsigned now;  // relaxed polls, one acquire fence once the generation has moved
@@ -141,7 +150,7 @@ __device__ __forceinline__ bool grid_barrier(unsigned* bar, unsigned n_ctas, uns
       asm volatile("fence.acq_rel.gpu;" ::: "memory");
       return true;
     }
-    if ((spin & 15u) == 0u && (*abort_flag || clock64() - t_start > limit)) {
+    if ((spin & 15u) == 0u && (*abort_flag || global_timer_ns() - t_start > limit)) {
       atomicSub(bar, 1u);
       *abort_flag = 1;
       return false;

@@ -57,12 +57,15 @@ def _first_use(device: torch.device, status: torch.Tensor) -> None:
     """One throw-away forward + backward per kernel instantiation (head dims 64 and 128) the first
     time a device is used, then the status word is cleared.
 
-    Why: on some B200 hosts the very first launch of the 64-wide kernel in a fresh process ran into
-    its 0.4 s wait limit (about one fresh process in ten on two hosts, never on three others, never
-    in any later launch: 11,000 consecutive steps clean); the cause has not been found. The library's
-    module load, the switch of the SMs to its shared-memory configuration and the cold instruction
-    caches all fall on that launch. Taking it on 160 heads of 128 tokens whose results nobody reads keeps a
-    caller's first real call from being the one that is lost. Skipped while a stream is being
+    Why: on some B200 hosts the very first launch of the 64-wide kernel in a process that started
+    right after another one had exited ran into its wait limit (then 0.4 s of the SM's cycle counter;
+    about one fresh process in ten on two hosts, never on three others, never in any later launch).
+    The likely cause is preemption: the kernel shares the GPU with the previous process's context
+    while that is being torn down, and a CTA that is switched out keeps "waiting" by the clock, or
+    resumes on another SM whose cycle counter is unrelated. The waits are timed with the global
+    timer and allowed 2 s since; this launch on 160 heads of 128 tokens, whose results nobody reads,
+    additionally keeps the module load, the SMs' switch to the kernel's shared-memory configuration
+    and the cold instruction caches off a caller's first real call. Skipped while a stream is being
     captured (nothing may synchronise then)."""
     if torch.cuda.is_current_stream_capturing():
         return

@@ -120,8 +120,9 @@ typedef struct FlaArgs {
    * fp32. Mind the range: the unnormalised product grows with the sequence and fp16 ends at 65504. */
   int32_t dtype;
 
-  /* Limit of one device-side wait in microseconds (converted with the nominal SM clock);
-   * 0 = the default of about 0.4 s. Legitimate waits of these kernels last microseconds. */
+  /* Limit of one device-side wait in microseconds of the GPU's global timer; 0 = the default of
+   * 2 s. Legitimate waits of these kernels last microseconds; the default leaves room for a kernel
+   * that is switched out for another context's time slice on a shared GPU. */
   uint32_t wait_limit_us;
   /* FLA_DEBUG_* bits, 0 in production. */
   uint32_t debug_flags;
