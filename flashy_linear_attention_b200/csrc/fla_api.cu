@@ -263,8 +263,8 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_relaxed_sys(unsigned* p, unsigned v) {
-  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
@@ -298,14 +298,17 @@ __global__ void fla_state_exchange_kernel(const ExchangeParams xp) {
     for (int d = 0; d < xp.world; ++d)
       if (d != xp.rank) xp.inbox[d][slot] = total;
   }
-  // Every thread orders its stores before anything it (or, through the barrier, thread d) writes
-  // afterwards, at system scope; then thread d raises this block's flag in peer d's inbox. One
-  // fence per thread and the flag stores of all peers in flight together.
+  // Every thread waits for its own stores to be performed at system scope (so that the waits for
+  // the NVLink acknowledgements run side by side, not one after the other in the flag writers);
+  // then thread d raises this block's flag in peer d's inbox with a RELEASE store: the barrier
+  // puts the whole block's stores before it, and the release is what carries them to the peer's
+  // acquire load (a fence that thread d executed before the barrier would not cover the other
+  // threads' stores). The flag stores of all peers are in flight together.
   __threadfence_system();
   __syncthreads();
   if (static_cast<int>(threadIdx.x) < xp.world && static_cast<int>(threadIdx.x) != xp.rank) {
     const size_t f = (static_cast<size_t>(parity) * xp.world + xp.rank) * nblocks + block_id;
-    st_relaxed_sys(xp.flags[threadIdx.x] + f, epoch);
+    st_release_sys(xp.flags[threadIdx.x] + f, epoch);
   }
   // 3. wait (bounded) for the same block of every other rank. Waiting for all of them, not only the
   //    ones whose totals are needed, keeps any rank from running two exchanges ahead of another,

@@ -996,7 +996,7 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
           const bool masked0 = kUpper ? (cb0 < quad) : (cb0 > quad);  // warp-uniform
           const bool masked1 = kUpper ? (cb1 < quad) : (cb1 > quad);
           // both blocks are fetched before either is converted: the two TMEM loads are in flight
-          // together and issuer X gets the fp32 tile back as early as possible
+          // together
           if (!masked0 && !masked1) {
             ptx::tmem_ld32x2(lane_base + cfg::P_COL + cb0 * 32, ra, lane_base + cfg::P_COL + cb1 * 32, rb);
           } else if (!masked0) {
@@ -1004,8 +1004,6 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
           } else if (!masked1) {
             ptx::tmem_ld32(lane_base + cfg::P_COL + cb1 * 32, rb);
           }
-          ptx::tc_fence_before();
-          ptx::mbar_arrive(p_read);
           auto convert_block = [&](int cb, bool masked, const uint32_t (&r)[32]) {
             if (masked) {
 #pragma unroll
@@ -1035,6 +1033,14 @@ fla_chunk_kernel(const __grid_constant__ KernelParams p) {
           };
           convert_block(cb0, masked0, ra);
           convert_block(cb1, masked1, rb);
+          // Issuer X may overwrite the fp32 tile now. The arrival comes AFTER the conversions, which
+          // consume every loaded register: placed directly behind the load (and its
+          // tcgen05.wait::ld) it was observed to let X's next score MMA overwrite columns that the
+          // second of the two loads had not delivered yet -- rarely, when X was already polling
+          // this barrier (first chunk of a CTA), and the block then held a mix of this chunk's and
+          // the next chunk's scores.
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(p_read);
         };
         if (tms && !plain_chunk(i)) {
           p_convert(std::integral_constant<int, 2>{});

@@ -388,8 +388,6 @@ fla_wide_kernel(const __grid_constant__ WideParams p) {
         pk[j] = ptx::pack_bf16x2(__uint_as_float(ra[2 * j]), __uint_as_float(ra[2 * j + 1]));
         pk[16 + j] = ptx::pack_bf16x2(__uint_as_float(rb[2 * j]), __uint_as_float(rb[2 * j + 1]));
       }
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(o_free);
       if (lane == 0) ptx::bulk_wait_group_read0();  // the previous store has read these rows
       __syncwarp();
       const uint32_t obuf = ost_addr + row * 128;
@@ -397,6 +395,10 @@ fla_wide_kernel(const __grid_constant__ WideParams p) {
       for (int j = 0; j < 8; ++j)
         ptx::st_shared_v4(obuf + ((static_cast<uint32_t>(j) ^ swz) << 4), pk[j * 4], pk[j * 4 + 1],
                           pk[j * 4 + 2], pk[j * 4 + 3]);
+      // the accumulator may be overwritten: signalled after the stores that consume every loaded
+      // register (an arrival directly behind a TMEM load does not reliably wait for its data)
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(o_free);
       ptx::fence_proxy_async_smem();
       __syncwarp();
       const int tok = mem_chunk(i) * kWideChunk + quad * 32;
